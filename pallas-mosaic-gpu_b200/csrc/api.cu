@@ -1,0 +1,100 @@
+// extern "C" entry points of libsplash_sm100.so: argument validation, dispatch to
+// the compiled kernel configuration, status helpers.
+#include "dispatch.h"
+#include "host_common.cuh"
+
+namespace splash {
+
+static int check_common(const SplashParams* p, bool backward) {
+  if (!p) return fail(SPLASH_INVALID_ARGUMENT, "params is null");
+  if (!p->q || !p->k || !p->v || !p->status) return fail(SPLASH_INVALID_ARGUMENT, "q, k, v and status must be non-null");
+  if (!p->num_steps || !p->block_order || !p->block_list || !p->block_kind)
+    return fail(SPLASH_INVALID_ARGUMENT, "schedule arrays must be non-null");
+  if (p->batch <= 0 || p->heads <= 0 || p->kv_heads <= 0 || p->q_len <= 0 || p->kv_len <= 0)
+    return fail(SPLASH_INVALID_ARGUMENT, "sizes must be positive");
+  if (p->heads % p->kv_heads) return fail(SPLASH_INVALID_ARGUMENT, "heads not a multiple of kv_heads");
+  if (p->dtype != SPLASH_DTYPE_BF16 && p->dtype != SPLASH_DTYPE_F16) return fail(SPLASH_UNSUPPORTED, "Only bf16/f16 are supported");
+  if (p->head_dim % 64 || p->head_dim_v % 64 || p->head_dim > 256 || p->head_dim_v > 256 || p->head_dim <= 0 ||
+      p->head_dim_v <= 0)
+    return fail(SPLASH_UNSUPPORTED, "head dims must be multiples of 64 and <= 256");
+  if (p->mask_heads != 1 && p->mask_heads != p->heads) return fail(SPLASH_INVALID_ARGUMENT, "mask_heads must be 1 or heads");
+  if (p->max_steps < 1) return fail(SPLASH_INVALID_ARGUMENT, "max_steps must be >= 1");
+  if ((p->seg_q == nullptr) != (p->seg_kv == nullptr)) return fail(SPLASH_INVALID_ARGUMENT, "seg_q and seg_kv go together");
+  if (p->partial_blocks && (!p->mask_block || p->num_partial_blocks <= 0))
+    return fail(SPLASH_INVALID_ARGUMENT, "dense partial blocks need mask_block ids");
+  if (p->partial_blocks && p->mask_desc) return fail(SPLASH_INVALID_ARGUMENT, "give dense partial blocks or a band descriptor, not both");
+  if (static_cast<int64_t>(p->batch) * p->heads * p->q_len >= (1ll << 31) ||
+      static_cast<int64_t>(p->batch) * p->kv_heads * p->kv_len >= (1ll << 31))
+    return fail(SPLASH_INVALID_ARGUMENT, "batch * heads * length must fit in 31 bits");
+  if (backward && (!p->d_out || !p->lse || !p->delta)) return fail(SPLASH_INVALID_ARGUMENT, "backward needs d_out, lse and delta");
+  return SPLASH_OK;
+}
+
+static int check_fwd(const SplashParams* p, int tiles) {
+  if (int rc = check_common(p, false)) return rc;
+  if (!p->out) return fail(SPLASH_INVALID_ARGUMENT, "out is null");
+  if (p->block_q != 128 * tiles) return fail(SPLASH_INVALID_ARGUMENT, "block_q does not match this entry point");
+  if (p->block_kv != 64 && p->block_kv != 128) return fail(SPLASH_INVALID_ARGUMENT, "block_kv must be 64 or 128");
+  if (p->num_stages < 2 || p->num_stages > 8) return fail(SPLASH_INVALID_ARGUMENT, "num_stages must be in [2, 8]");
+  if (p->q_len % p->block_q || p->kv_len % p->block_kv)
+    return fail(SPLASH_INVALID_ARGUMENT, "Sequence lengths must be multiples of the block sizes");
+  return SPLASH_OK;
+}
+
+#define SPLASH_FWD_CASE(D_, DV_, NT_)                                                               \
+  if (p->head_dim == D_ && p->head_dim_v == DV_) {                                                  \
+    return p->block_kv == 64 ? launch_fwd<D_, DV_, 64, NT_>(*p, st) : launch_fwd<D_, DV_, 128, NT_>(*p, st); \
+  }
+
+}  // namespace splash
+
+using namespace splash;
+
+extern "C" int splash_fwd128(const SplashParams* p, void* stream) {
+  if (int rc = check_fwd(p, 1)) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  SPLASH_FWD_CASE(64, 64, 1)
+  SPLASH_FWD_CASE(64, 128, 1)
+  SPLASH_FWD_CASE(128, 128, 1)
+  SPLASH_FWD_CASE(128, 64, 1)
+  SPLASH_FWD_CASE(192, 192, 1)
+  SPLASH_FWD_CASE(256, 256, 1)
+  return fail(SPLASH_UNSUPPORTED, "this (head_dim, head_dim_v) pair is not compiled for the 128-row forward");
+}
+
+extern "C" int splash_fwd256(const SplashParams* p, void* stream) {
+  if (int rc = check_fwd(p, 2)) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (p->head_dim != p->head_dim_v) return fail(SPLASH_UNSUPPORTED, "ping-pong kernel needs head_dim == head_dim_v");
+  SPLASH_FWD_CASE(64, 64, 2)
+  SPLASH_FWD_CASE(128, 128, 2)
+  return fail(SPLASH_UNSUPPORTED, "ping-pong kernel supports head_dim 64/128");
+}
+
+extern "C" int splash_read_status(const int32_t* status, int32_t* host_out, void* stream) {
+  int32_t h[4] = {0, 0, 0, 0};
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  SPLASH_CUDA_CHECK(cudaMemcpyAsync(h, status, sizeof h, cudaMemcpyDeviceToHost, st));
+  SPLASH_CUDA_CHECK(cudaStreamSynchronize(st));
+  if (host_out) memcpy(host_out, h, sizeof h);
+  if (h[0] != 0) {
+    char d[128];
+    snprintf(d, sizeof d, "code %d at wait site %d, block %d, step %d", h[0], h[1], h[2], h[3]);
+    return fail(SPLASH_DEVICE_TIMEOUT, "a kernel gave up waiting", d);
+  }
+  return SPLASH_OK;
+}
+
+extern "C" const char* splash_status_string(int status) {
+  switch (status) {
+    case SPLASH_OK: return "ok";
+    case SPLASH_INVALID_ARGUMENT: return "invalid argument";
+    case SPLASH_UNSUPPORTED: return "unsupported configuration";
+    case SPLASH_BUDGET_EXCEEDED: return "shared/tensor memory budget exceeded";
+    case SPLASH_CUDA_ERROR: return "CUDA error";
+    case SPLASH_DEVICE_TIMEOUT: return "device-side wait timed out";
+    default: return "unknown status";
+  }
+}
+
+extern "C" const char* splash_last_error(void) { return last_error_buf(); }

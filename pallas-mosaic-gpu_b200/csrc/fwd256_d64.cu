@@ -1,0 +1,6 @@
+// Explicit instantiations of the forward launcher (see fwd_launch.cuh).
+#include "fwd_launch.cuh"
+namespace splash {
+template int launch_fwd<64, 64, 64, 2>(const SplashParams&, cudaStream_t);
+template int launch_fwd<64, 64, 128, 2>(const SplashParams&, cudaStream_t);
+}  // namespace splash

@@ -1,0 +1,550 @@
+// Splash attention forward for sm_100a: one warp-specialised kernel template that
+// covers both forward variants.
+//
+//   NT = 1  one 128-row q tile per CTA.  The two S buffers in tensor memory
+//           alternate between KV steps, so Q.K^T of step s+1 runs while the
+//           softmax warpgroup works on step s.
+//   NT = 2  two 128-row q tiles per CTA ("ping-pong").  Each tile has its own S
+//           buffer and its own softmax warpgroup; every K/V block fetched is
+//           used by both tiles, and the tensor core works for one tile while the
+//           other tile's softmax runs.
+//
+// Roles inside a CTA
+//   softmax warpgroup(s)  warps [0, 4*NT): one thread per q row (= TMEM lane)
+//   TMA producer          warp 4*NT, lane 0: Q once, then K, V (+ KV segment ids,
+//                         + the int8 block of a dense partial mask) per visited block
+//   MMA issuer            warp 4*NT+1, lane 0: all tcgen05.mma / commit
+//
+// Data flow per visited KV block:  S = Q K^T (smem x smem -> TMEM f32), softmax in
+// registers (exp2 domain, running max kept stale until it moves by more than 2^8),
+// P written back over S as packed 16-bit, O += P V (TMEM x smem -> TMEM f32).
+// Empty blocks are never touched, FULL blocks skip masking, PARTIAL blocks are
+// masked in registers from a band descriptor or a dense int8 block.
+//
+// Behaviour follows the reference kernels (splash_attention_mgpu/kernel.py:132-537,
+// forward_pingpong.py:131-681); the code shares nothing with them.
+#pragma once
+
+#include <stddef.h>
+
+#include "../../include/splash_sm100.h"
+#include "ptx.cuh"
+
+namespace splash {
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr float kRescaleThreshold = 8.0f;  // in powers of two
+
+struct FwdArgs {
+  const int32_t* num_steps;
+  const int32_t* block_order;
+  const int32_t* block_list;
+  const int32_t* block_kind;
+  const int32_t* mask_block;
+  const int32_t* mask_desc;
+  const int32_t* seg_q;
+  const int32_t* seg_kv;
+  void* out;
+  float* lse_out;
+  int32_t* status;
+  int32_t batch, heads, kv_heads, q_len, kv_len;
+  int32_t mask_heads, max_steps, q_blocks, stages;
+  int32_t has_dense, has_seg;
+  float mask_value, soft_cap;
+};
+
+// Wait sites, reported in the status word when a wait runs out.
+enum FwdSite : int {
+  kSiteTmaKEmpty = 1, kSiteTmaVEmpty, kSiteTmaAuxEmpty,
+  kSiteMmaQ, kSiteMmaK, kSiteMmaV, kSiteMmaP,
+  kSiteSmxS, kSiteSmxAux, kSiteSmxPv, kSiteSmxDone, kSiteSmxEpi,
+};
+
+template <int D, int DV, int BKV, int NT>
+struct FwdLayout {
+  static constexpr int kTile = 128;
+  static constexpr int kQBytes = NT * kTile * D * 2;
+  static constexpr int kKStage = BKV * D * 2;
+  static constexpr int kVStage = BKV * DV * 2;
+  static constexpr int kMaskStage = NT * kTile * BKV;
+  static constexpr int kSegStage = BKV * 4;
+  static constexpr int kTmemUsed = 2 * BKV + NT * DV;
+  static constexpr int kTmemCols = kTmemUsed <= 128 ? 128 : (kTmemUsed <= 256 ? 256 : 512);
+  static constexpr int kThreads = (NT + 1) * 128;
+  static constexpr bool kOStageInQ = (NT == 2) || (DV <= D);
+  // Register split between the warpgroups of the two-tile kernel (multiples of 8;
+  // 2 * 128 * softmax + 128 * producer <= 64K).
+  static constexpr int kSoftmaxRegs = 216;
+  static constexpr int kProducerRegs = 72;
+
+  __host__ __device__ static size_t smem_bytes(int stages, bool dense, bool seg) {
+    size_t b = 1024;  // alignment slack
+    b += kQBytes + static_cast<size_t>(stages) * (kKStage + kVStage);
+    if (dense) b += static_cast<size_t>(stages) * kMaskStage;
+    if (seg) b += static_cast<size_t>(stages) * kSegStage;
+    b += 1024;  // barriers, TMEM slot, flags
+    return b;
+  }
+};
+
+constexpr int kFwdMaxStages = 8;
+
+struct FwdBarriers {
+  uint64_t q_full;
+  uint64_t k_full[kFwdMaxStages], k_empty[kFwdMaxStages];
+  uint64_t v_full[kFwdMaxStages], v_empty[kFwdMaxStages];
+  uint64_t aux_full[kFwdMaxStages], aux_empty[kFwdMaxStages];
+  uint64_t s_ready[2], p_ready[2];
+  uint64_t pv_done, o_done;
+  uint64_t epi[2];
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+  uint32_t dead;  // status word was already non-zero at entry
+};
+
+#define SPLASH_BAR(field, idx) \
+  (bars_u32 + static_cast<uint32_t>(offsetof(FwdBarriers, field)) + 8u * static_cast<uint32_t>(idx))
+
+template <int D, int DV, int BKV, int NT, bool BF16>
+__global__ void __launch_bounds__((NT + 1) * 128, 1)
+splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                  const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
+                  const __grid_constant__ CUtensorMap tm_mask, const FwdArgs a) {
+  using L = FwdLayout<D, DV, BKV, NT>;
+  constexpr int kTile = 128;
+  constexpr int kBq = NT * kTile;
+  constexpr int kSoftmaxWarps = 4 * NT;
+
+  extern __shared__ uint8_t smem_raw[];
+  const int stages = a.stages;
+  // Shared-window addresses (32-bit) of the buffers; tiles are 1024-byte aligned.
+  const uint32_t q_u32 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t k_u32 = q_u32 + L::kQBytes;
+  const uint32_t v_u32 = k_u32 + stages * L::kKStage;
+  const uint32_t mask_u32 = v_u32 + stages * L::kVStage;
+  const uint32_t seg_u32 = mask_u32 + (a.has_dense ? stages * L::kMaskStage : 0);
+  const uint32_t bars_u32 = seg_u32 + (a.has_seg ? stages * L::kSegStage : 0);
+  const uint32_t abort_u32 = bars_u32 + static_cast<uint32_t>(offsetof(FwdBarriers, abort_flag));
+  const uint32_t dead_u32 = bars_u32 + static_cast<uint32_t>(offsetof(FwdBarriers, dead));
+  const uint32_t tmem_slot_u32 = bars_u32 + static_cast<uint32_t>(offsetof(FwdBarriers, tmem_base));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // ---- which tile of work ---------------------------------------------------
+  const int hb_count = a.heads * a.batch;
+  const int order_idx = blockIdx.x / hb_count;  // heaviest q blocks of every head first
+  const int hb = blockIdx.x - order_idx * hb_count;
+  const int h = hb % a.heads;
+  const int b = hb / a.heads;
+  const int mh = a.mask_heads > 1 ? h : 0;
+  const int qi = a.block_order[mh * a.q_blocks + order_idx];
+  const int n = a.num_steps[mh * a.q_blocks + qi];
+  const bool has_aux = a.has_dense || a.has_seg;
+  const int sched_off = (mh * a.q_blocks + qi) * a.max_steps;  // offset into the step lists
+  const int q_row0 = (b * a.heads + h) * a.q_len + qi * kBq;   // row in the [B*H*Sq, D] view
+
+  // ---- set-up -----------------------------------------------------------------
+  if (threadIdx.x == 0) {
+    sts32(abort_u32, 0);
+    sts32(dead_u32, a.status[0] != 0);
+    mbar_init(SPLASH_BAR(q_full, 0), 1);
+    for (int i = 0; i < stages; ++i) {
+      mbar_init(SPLASH_BAR(k_full, i), 1);
+      mbar_init(SPLASH_BAR(k_empty, i), 1);
+      mbar_init(SPLASH_BAR(v_full, i), 1);
+      mbar_init(SPLASH_BAR(v_empty, i), 1);
+      mbar_init(SPLASH_BAR(aux_full, i), 1);
+      mbar_init(SPLASH_BAR(aux_empty, i), kSoftmaxWarps);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(SPLASH_BAR(s_ready, i), 1);
+      mbar_init(SPLASH_BAR(p_ready, i), kTile);
+      mbar_init(SPLASH_BAR(epi, i), kTile);
+    }
+    mbar_init(SPLASH_BAR(pv_done, 0), 1);
+    mbar_init(SPLASH_BAR(o_done, 0), 1);
+    fence_mbar_init();
+    fence_proxy_async_smem();
+  }
+  __syncthreads();
+  if (lds32(dead_u32)) return;
+  if (warp == kSoftmaxWarps + 1) {
+    tmem_alloc(tmem_slot_u32, L::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = lds32(tmem_slot_u32);
+  const WaitCtx ctx{abort_u32, a.status};
+
+  constexpr uint32_t kIdescQK = make_idesc(BF16, 128, BKV, false, false);
+  constexpr uint32_t kIdescPV = make_idesc(BF16, 128, DV, false, true);
+  constexpr uint32_t kDescHi = desc_hi(1024);
+
+  if (warp >= kSoftmaxWarps) {
+    // =========================== producer warpgroup ============================
+    if constexpr (NT == 2) setmaxnreg_dec<L::kProducerRegs>();
+    if (warp == kSoftmaxWarps && lane == 0 && n > 0) {
+      // ------------------------------ TMA producer ------------------------------
+      const int kv_row0 = (b * a.kv_heads + h / (a.heads / a.kv_heads)) * a.kv_len;
+      prefetch_tensormap(&tm_q);
+      prefetch_tensormap(&tm_k);
+      prefetch_tensormap(&tm_v);
+      mbar_arrive_expect_tx(SPLASH_BAR(q_full, 0), L::kQBytes);
+#pragma unroll
+      for (int t = 0; t < NT; ++t)
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_2d(q_u32 + t * (kTile * D * 2) + c * (kTile * 128), &tm_q, c * 64, q_row0 + t * kTile,
+                      SPLASH_BAR(q_full, 0));
+      int slot = 0;
+      uint32_t phase = 0;
+      int j_next = a.block_list[sched_off];
+      for (int s = 0; s < n; ++s) {
+        const int j = j_next;
+        if (s + 1 < n) j_next = a.block_list[sched_off + s + 1];
+        const int kv_row = kv_row0 + j * BKV;
+        if (s >= stages && !mbar_wait(SPLASH_BAR(k_empty, slot), phase ^ 1, ctx, kSiteTmaKEmpty, s)) break;
+        mbar_arrive_expect_tx(SPLASH_BAR(k_full, slot), L::kKStage);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_2d(k_u32 + slot * L::kKStage + c * (BKV * 128), &tm_k, c * 64, kv_row, SPLASH_BAR(k_full, slot));
+        if (s >= stages && !mbar_wait(SPLASH_BAR(v_empty, slot), phase ^ 1, ctx, kSiteTmaVEmpty, s)) break;
+        mbar_arrive_expect_tx(SPLASH_BAR(v_full, slot), L::kVStage);
+#pragma unroll
+        for (int c = 0; c < DV / 64; ++c)
+          tma_load_2d(v_u32 + slot * L::kVStage + c * (BKV * 128), &tm_v, c * 64, kv_row, SPLASH_BAR(v_full, slot));
+        if (has_aux) {
+          if (s >= stages && !mbar_wait(SPLASH_BAR(aux_empty, slot), phase ^ 1, ctx, kSiteTmaAuxEmpty, s)) break;
+          const bool partial_dense = a.has_dense && a.block_kind[sched_off + s] == SPLASH_BLOCK_PARTIAL;
+          const uint32_t bytes = (a.has_seg ? L::kSegStage : 0) + (partial_dense ? L::kMaskStage : 0);
+          mbar_arrive_expect_tx(SPLASH_BAR(aux_full, slot), bytes);
+          if (a.has_seg)
+            bulk_load_1d(seg_u32 + slot * L::kSegStage, a.seg_kv + static_cast<size_t>(b) * a.kv_len + j * BKV,
+                         L::kSegStage, SPLASH_BAR(aux_full, slot));
+          if (partial_dense) {
+            const int mrow = a.mask_block[sched_off + s] * kBq;
+#pragma unroll
+            for (int t = 0; t < NT; ++t)
+              tma_load_2d(mask_u32 + slot * L::kMaskStage + t * (kTile * BKV), &tm_mask, 0, mrow + t * kTile,
+                          SPLASH_BAR(aux_full, slot));
+          }
+        }
+        if (++slot == stages) { slot = 0; phase ^= 1; }
+      }
+    } else if (warp == kSoftmaxWarps + 1 && lane == 0 && n > 0) {
+      // ------------------------------- MMA issuer -------------------------------
+      // S_t = Q_t K^T: both operands K-major, 64-element (128-byte) boxes side by side.
+      auto issue_qk = [&](int t, int kslot, uint32_t s_dst) {
+        const uint32_t a_lo = desc_lo(q_u32 + t * (kTile * D * 2), 16);
+        const uint32_t b_lo = desc_lo(k_u32 + kslot * L::kKStage, 16);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t ao = ((kk / 4) * (kTile * 128) + (kk % 4) * 32) >> 4;
+          const uint32_t bo = ((kk / 4) * (BKV * 128) + (kk % 4) * 32) >> 4;
+          umma_ss2(s_dst, a_lo + ao, kDescHi, b_lo + bo, kDescHi, kIdescQK, kk > 0);
+        }
+      };
+      // O_t (+)= P_t V: P from tensor memory (8 columns per 16 keys), V MN-major.
+      auto issue_pv = [&](int t, int vslot, uint32_t p_src, uint32_t acc) {
+        const uint32_t b_lo = desc_lo(v_u32 + vslot * L::kVStage, BKV * 128);
+#pragma unroll
+        for (int kk = 0; kk < BKV / 16; ++kk)
+          umma_ts2(tmem + 2 * BKV + t * DV, p_src + kk * 8, b_lo + ((kk * 2048) >> 4), kDescHi, kIdescPV,
+                   kk > 0 ? 1u : acc);
+      };
+      bool ok = mbar_wait(SPLASH_BAR(q_full, 0), 0, ctx, kSiteMmaQ, 0) &&
+                mbar_wait(SPLASH_BAR(k_full, 0), 0, ctx, kSiteMmaK, 0);
+      if (ok) {
+        tc_fence_after();
+        issue_qk(0, 0, tmem);
+        umma_commit(SPLASH_BAR(s_ready, 0));
+        if constexpr (NT == 2) {
+          issue_qk(1, 0, tmem + BKV);
+          umma_commit(SPLASH_BAR(s_ready, 1));
+        }
+        umma_commit(SPLASH_BAR(k_empty, 0));
+        int slot = 0;
+        uint32_t phase = 0;
+        for (int s = 0; s < n; ++s) {
+          int slot1 = slot + 1;
+          uint32_t phase1 = phase;
+          if (slot1 == stages) { slot1 = 0; phase1 ^= 1; }
+          const bool next = s + 1 < n;
+          if constexpr (NT == 1) {
+            const int cur = s & 1;
+            if (next) {
+              if (!mbar_wait(SPLASH_BAR(k_full, slot1), phase1, ctx, kSiteMmaK, s + 1)) break;
+              tc_fence_after();
+              issue_qk(0, slot1, tmem + (cur ^ 1) * BKV);
+              umma_commit(SPLASH_BAR(s_ready, cur ^ 1));
+              umma_commit(SPLASH_BAR(k_empty, slot1));
+            }
+            if (!mbar_wait(SPLASH_BAR(v_full, slot), phase, ctx, kSiteMmaV, s)) break;
+            if (!mbar_wait(SPLASH_BAR(p_ready, cur), (s >> 1) & 1, ctx, kSiteMmaP, s)) break;
+            tc_fence_after();
+            issue_pv(0, slot, tmem + cur * BKV, s > 0);
+            umma_commit(SPLASH_BAR(v_empty, slot));
+            umma_commit(SPLASH_BAR(pv_done, 0));
+          } else {
+            if (!mbar_wait(SPLASH_BAR(v_full, slot), phase, ctx, kSiteMmaV, s)) break;
+            if (!mbar_wait(SPLASH_BAR(p_ready, 0), s & 1, ctx, kSiteMmaP, s)) break;
+            tc_fence_after();
+            issue_pv(0, slot, tmem, s > 0);
+            if (next) {
+              if (!mbar_wait(SPLASH_BAR(k_full, slot1), phase1, ctx, kSiteMmaK, s + 1)) break;
+              tc_fence_after();
+              issue_qk(0, slot1, tmem);
+              umma_commit(SPLASH_BAR(s_ready, 0));
+            }
+            if (!mbar_wait(SPLASH_BAR(p_ready, 1), s & 1, ctx, kSiteMmaP, s)) break;
+            tc_fence_after();
+            issue_pv(1, slot, tmem + BKV, s > 0);
+            umma_commit(SPLASH_BAR(v_empty, slot));
+            if (next) {
+              issue_qk(1, slot1, tmem + BKV);
+              umma_commit(SPLASH_BAR(s_ready, 1));
+              umma_commit(SPLASH_BAR(k_empty, slot1));
+            }
+          }
+          slot = slot1;
+          phase = phase1;
+        }
+        if constexpr (NT == 2) umma_commit(SPLASH_BAR(o_done, 0));
+      }
+    }
+  } else {
+    // ============================ softmax warpgroups ============================
+    if constexpr (NT == 2) setmaxnreg_inc<L::kSoftmaxRegs>();
+    const int t = warp >> 2;                       // which q tile
+    const int row = (warp & 3) * 32 + lane;        // row inside the tile
+    const int q_pos = qi * kBq + t * kTile + row;  // position in the sequence
+    // TMEM address of this thread's lane quarter, column 0.
+    const uint32_t tmem_row = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+    const uint32_t o_tmem = tmem_row + 2 * BKV + t * DV;
+
+    if (n == 0) {
+      // No visible block: zeros and lse = mask_value, nothing else runs.
+      const size_t out_row = static_cast<size_t>(q_row0) + t * kTile + row;
+      const uint4 z = make_uint4(0, 0, 0, 0);
+      uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(a.out) + out_row * (DV * 2));
+#pragma unroll
+      for (int c = 0; c < DV * 2 / 16; ++c) dst[c] = z;
+      if (a.lse_out) a.lse_out[out_row] = a.mask_value;
+    } else {
+      // Per-row band in units of (kv_pos - q_pos); a chunk restriction folds in.
+      int band_lo = -(1 << 30), band_hi = (1 << 30);
+      if (a.mask_desc) {
+        band_lo = a.mask_desc[mh * 4 + 0];
+        band_hi = a.mask_desc[mh * 4 + 1];
+        const int chunk = a.mask_desc[mh * 4 + 2];
+        if (chunk > 0) {
+          const int start = (q_pos / chunk) * chunk;
+          band_lo = max(band_lo, start - q_pos);
+          band_hi = min(band_hi, start + chunk - 1 - q_pos);
+        }
+      }
+      const int my_seg = a.has_seg ? a.seg_q[static_cast<size_t>(b) * a.q_len + q_pos] : 0;
+
+      float m_run = -INFINITY;  // stale running max, raw logit units
+      float l_run = 0.f;
+      int slot = 0;
+      uint32_t phase = 0;
+      int kind = a.block_kind[sched_off];
+      int jblk = a.block_list[sched_off];
+      bool alive = true;
+
+      for (int s = 0; s < n; ++s) {
+        const int kind_now = kind, j_now = jblk;
+        if (s + 1 < n) {
+          kind = a.block_kind[sched_off + s + 1];
+          jblk = a.block_list[sched_off + s + 1];
+        }
+        const int buf = (NT == 2) ? t : (s & 1);
+        const uint32_t par = (NT == 2) ? (s & 1) : ((s >> 1) & 1);
+        const uint32_t s_tmem = tmem_row + buf * BKV;
+        if (!warp_wait(SPLASH_BAR(s_ready, buf), par, ctx, kSiteSmxS, s)) { alive = false; break; }
+        tc_fence_after();
+        float sv[BKV];
+        {
+          uint32_t* raw = reinterpret_cast<uint32_t*>(sv);
+#pragma unroll
+          for (int c = 0; c < BKV / 32; ++c) tmem_ld32(s_tmem + c * 32, raw + c * 32);
+          tmem_wait_ld();
+        }
+        if (a.soft_cap > 0.f) {
+          const float cap = a.soft_cap, inv_cap = 1.f / a.soft_cap;
+#pragma unroll
+          for (int i = 0; i < BKV; ++i) sv[i] = cap * tanh_approx(sv[i] * inv_cap);
+        }
+        if (has_aux) {
+          if (!warp_wait(SPLASH_BAR(aux_full, slot), phase, ctx, kSiteSmxAux, s)) { alive = false; break; }
+        }
+        const bool partial = kind_now == SPLASH_BLOCK_PARTIAL;
+        if (partial && !a.has_dense) {
+          const int d0 = j_now * BKV - q_pos;
+#pragma unroll
+          for (int i = 0; i < BKV; ++i) {
+            const int d = d0 + i;
+            if (d < band_lo || d > band_hi) sv[i] = -INFINITY;
+          }
+        }
+        if (partial && a.has_dense) {
+          const uint32_t mrow = mask_u32 + slot * L::kMaskStage + t * (kTile * BKV);
+#pragma unroll
+          for (int c = 0; c < BKV / 16; ++c) {
+            uint32_t off = row * BKV + c * 16;
+            off ^= ((off >> 7) & (BKV == 128 ? 7u : 3u)) << 4;  // TMA swizzle of the mask tile
+            const uint4 w = lds128(mrow + off);
+            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int e = 0; e < 16; ++e)
+              if (((ww[e >> 2] >> ((e & 3) * 8)) & 0xff) == 0) sv[c * 16 + e] = -INFINITY;
+          }
+        }
+        if (a.has_seg) {
+          const uint32_t segs = seg_u32 + slot * L::kSegStage;
+#pragma unroll
+          for (int c = 0; c < BKV / 4; ++c) {
+            const uint4 g = lds128(segs + c * 16);
+            if (static_cast<int>(g.x) != my_seg) sv[c * 4 + 0] = -INFINITY;
+            if (static_cast<int>(g.y) != my_seg) sv[c * 4 + 1] = -INFINITY;
+            if (static_cast<int>(g.z) != my_seg) sv[c * 4 + 2] = -INFINITY;
+            if (static_cast<int>(g.w) != my_seg) sv[c * 4 + 3] = -INFINITY;
+          }
+        }
+        if (has_aux) {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(SPLASH_BAR(aux_empty, slot));
+        }
+
+        // ---- online softmax with a stale maximum --------------------------------
+        float mx0 = sv[0], mx1 = sv[1], mx2 = sv[2], mx3 = sv[3];
+#pragma unroll
+        for (int i = 4; i < BKV; i += 4) {
+          mx0 = fmaxf(mx0, sv[i]);
+          mx1 = fmaxf(mx1, sv[i + 1]);
+          mx2 = fmaxf(mx2, sv[i + 2]);
+          mx3 = fmaxf(mx3, sv[i + 3]);
+        }
+        const float m_new = fmaxf(m_run, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
+        const bool moved = (m_new - m_run) * kLog2e > kRescaleThreshold;  // false for NaN (-inf - -inf)
+        float alpha = 1.f;
+        if (moved) {
+          alpha = ex2_approx((m_run - m_new) * kLog2e);  // 0 when m_run was -inf
+          m_run = m_new;
+          l_run *= alpha;
+        }
+        const float m_scaled = (m_run == -INFINITY) ? 0.f : m_run * kLog2e;
+        float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+        // P goes over the S it came from, 32 columns of S (16 packed words) at a time
+        // so that only one small staging group is live beside the row itself.
+#pragma unroll
+        for (int c = 0; c < BKV / 32; ++c) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            const float p0 = ex2_approx(fmaf(sv[c * 32 + i], kLog2e, -m_scaled));
+            const float p1 = ex2_approx(fmaf(sv[c * 32 + i + 1], kLog2e, -m_scaled));
+            const float p2 = ex2_approx(fmaf(sv[c * 32 + i + 2], kLog2e, -m_scaled));
+            const float p3 = ex2_approx(fmaf(sv[c * 32 + i + 3], kLog2e, -m_scaled));
+            sum0 += p0;
+            sum1 += p1;
+            sum2 += p2;
+            sum3 += p3;
+            pk[i / 2] = pack2<BF16>(p0, p1);
+            pk[i / 2 + 1] = pack2<BF16>(p2, p3);
+          }
+          tmem_st16(s_tmem + c * 16, pk);
+        }
+        l_run += (sum0 + sum1) + (sum2 + sum3);
+
+        // O may only be touched once P.V of the previous step has finished.  With two
+        // tiles the s_ready wait above already certifies that (the tensor core runs
+        // its instructions in issue order); with one tile it is signalled explicitly.
+        if constexpr (NT == 1) {
+          if (s > 0 && !warp_wait(SPLASH_BAR(pv_done, 0), (s - 1) & 1, ctx, kSiteSmxPv, s)) { alive = false; break; }
+        }
+        if (s > 0 && __any_sync(0xffffffffu, moved)) {
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < DV / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld32(o_tmem + c * 32, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st32(o_tmem + c * 32, o);
+          }
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(SPLASH_BAR(p_ready, buf));
+        if (++slot == stages) { slot = 0; phase ^= 1; }
+      }
+
+      // ---- epilogue: O / l, cast, stage in shared memory, TMA store ---------------
+      if (alive) {
+        if constexpr (NT == 2) alive = warp_wait(SPLASH_BAR(o_done, 0), 0, ctx, kSiteSmxDone, n);
+        else alive = warp_wait(SPLASH_BAR(pv_done, 0), (n - 1) & 1, ctx, kSiteSmxDone, n);
+      }
+      if (alive) {
+        tc_fence_after();
+        const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
+        const uint32_t stage = L::kOStageInQ ? (q_u32 + t * (kTile * D * 2)) : v_u32;
+#pragma unroll
+        for (int c = 0; c < DV / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld32(o_tmem + c * 32, o);
+          tmem_wait_ld();
+          const uint32_t box = stage + (c / 2) * (kTile * 128);
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 w;
+            w.x = pack2<BF16>(__uint_as_float(o[g * 8 + 0]) * inv_l, __uint_as_float(o[g * 8 + 1]) * inv_l);
+            w.y = pack2<BF16>(__uint_as_float(o[g * 8 + 2]) * inv_l, __uint_as_float(o[g * 8 + 3]) * inv_l);
+            w.z = pack2<BF16>(__uint_as_float(o[g * 8 + 4]) * inv_l, __uint_as_float(o[g * 8 + 5]) * inv_l);
+            w.w = pack2<BF16>(__uint_as_float(o[g * 8 + 6]) * inv_l, __uint_as_float(o[g * 8 + 7]) * inv_l);
+            sts128(box + swz128(row, (c & 1) * 4 + g), w);
+          }
+        }
+        if (a.lse_out)
+          a.lse_out[static_cast<size_t>(q_row0) + t * kTile + row] =
+              l_run > 0.f ? m_run + lg2_approx(l_run) * kLn2 : a.mask_value;
+        fence_proxy_async_smem();
+        mbar_arrive(SPLASH_BAR(epi, t));
+        if (row == 0) {
+          if (mbar_wait(SPLASH_BAR(epi, t), 0, ctx, kSiteSmxEpi, n)) {
+#pragma unroll
+            for (int c = 0; c < DV / 64; ++c)
+              tma_store_2d(&tm_o, stage + c * (kTile * 128), c * 64, q_row0 + t * kTile);
+            bulk_commit_group();
+            bulk_wait_group<0>();
+          }
+        }
+      }
+    }
+  }
+
+  // ---- teardown: every thread of every role ends up here --------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (lds32(abort_u32)) {
+    // Give copies that were still in flight time to land before the CTA's shared
+    // memory is handed to another CTA.
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000) {}
+  }
+  if (warp == kSoftmaxWarps + 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem, L::kTmemCols);
+  }
+}
+
+#undef SPLASH_BAR
+
+}  // namespace splash

@@ -1,0 +1,82 @@
+// Host launcher for the forward kernel template: builds the TMA tensor maps for one
+// call and enqueues the grid.  Included by the translation units that instantiate
+// the kernel for a given (head_dim, head_dim_v, block_kv, tiles) combination.
+#pragma once
+
+#include "fwd_kernel.cuh"
+#include "host_common.cuh"
+
+namespace splash {
+
+template <int D, int DV, int BKV, int NT, bool BF16>
+int launch_fwd_typed(const SplashParams& p, cudaStream_t stream) {
+  using L = FwdLayout<D, DV, BKV, NT>;
+  const bool dense = p.partial_blocks != nullptr;
+  const bool seg = p.seg_q != nullptr;
+  const size_t smem = L::smem_bytes(p.num_stages, dense, seg);
+  if (smem > kMaxDynamicSmem) {
+    char d[96];
+    snprintf(d, sizeof d, "%zu > %zu bytes; reduce num_stages or block_kv", smem, kMaxDynamicSmem);
+    return fail(SPLASH_BUDGET_EXCEEDED, "Shared memory budget exceeded", d);
+  }
+  if (!L::kOStageInQ && p.num_stages * BKV < 128)
+    return fail(SPLASH_BUDGET_EXCEEDED, "Shared memory budget exceeded", "output staging needs num_stages * block_kv >= 128");
+
+  const CUtensorMapDataType dt = tmap_dtype(p.dtype);
+  const uint64_t q_rows = static_cast<uint64_t>(p.batch) * p.heads * p.q_len;
+  const uint64_t kv_rows = static_cast<uint64_t>(p.batch) * p.kv_heads * p.kv_len;
+  CUtensorMap tm_q, tm_k, tm_v, tm_o, tm_mask;
+  memset(&tm_mask, 0, sizeof tm_mask);
+  int rc;
+  if ((rc = make_tmap_2d(&tm_q, p.q, dt, 2, q_rows, D, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  if ((rc = make_tmap_2d(&tm_k, p.k, dt, 2, kv_rows, D, BKV, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  if ((rc = make_tmap_2d(&tm_v, p.v, dt, 2, kv_rows, DV, BKV, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  if ((rc = make_tmap_2d(&tm_o, p.out, dt, 2, q_rows, DV, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  if (dense) {
+    const uint64_t mrows = static_cast<uint64_t>(p.num_partial_blocks) * p.block_q;
+    if ((rc = make_tmap_2d(&tm_mask, p.partial_blocks, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, mrows, BKV, 128, BKV,
+                           BKV == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B)))
+      return rc;
+  }
+
+  FwdArgs a;
+  a.num_steps = p.num_steps;
+  a.block_order = p.block_order;
+  a.block_list = p.block_list;
+  a.block_kind = p.block_kind;
+  a.mask_block = p.mask_block;
+  a.mask_desc = p.mask_desc;
+  a.seg_q = p.seg_q;
+  a.seg_kv = p.seg_kv;
+  a.out = p.out;
+  a.lse_out = p.lse_out;
+  a.status = p.status;
+  a.batch = p.batch;
+  a.heads = p.heads;
+  a.kv_heads = p.kv_heads;
+  a.q_len = p.q_len;
+  a.kv_len = p.kv_len;
+  a.mask_heads = p.mask_heads;
+  a.max_steps = p.max_steps;
+  a.q_blocks = p.q_len / (128 * NT);
+  a.stages = p.num_stages;
+  a.has_dense = dense;
+  a.has_seg = seg;
+  a.mask_value = p.mask_value;
+  a.soft_cap = p.soft_cap;
+
+  auto kernel = splash_fwd_kernel<D, DV, BKV, NT, BF16>;
+  if ((rc = opt_in_smem(kernel, smem))) return rc;
+  const unsigned grid = static_cast<unsigned>(a.q_blocks) * p.heads * p.batch;
+  kernel<<<grid, L::kThreads, smem, stream>>>(tm_q, tm_k, tm_v, tm_o, tm_mask, a);
+  SPLASH_CUDA_CHECK(cudaGetLastError());
+  return SPLASH_OK;
+}
+
+template <int D, int DV, int BKV, int NT>
+int launch_fwd(const SplashParams& p, cudaStream_t stream) {
+  if (p.dtype == SPLASH_DTYPE_BF16) return launch_fwd_typed<D, DV, BKV, NT, true>(p, stream);
+  return launch_fwd_typed<D, DV, BKV, NT, false>(p, stream);
+}
+
+}  // namespace splash
