@@ -5,6 +5,8 @@
 
 namespace splash {
 
+constexpr int kBwdStagesMax = 4;
+
 static int check_common(const SplashParams* p, bool backward) {
   if (!p) return fail(SPLASH_INVALID_ARGUMENT, "params is null");
   if (!p->q || !p->k || !p->v || !p->status) return fail(SPLASH_INVALID_ARGUMENT, "q, k, v and status must be non-null");
@@ -69,6 +71,67 @@ extern "C" int splash_fwd256(const SplashParams* p, void* stream) {
   SPLASH_FWD_CASE(64, 64, 2)
   SPLASH_FWD_CASE(128, 128, 2)
   return fail(SPLASH_UNSUPPORTED, "ping-pong kernel supports head_dim 64/128");
+}
+
+static int check_bwd(const SplashParams* p) {
+  if (int rc = check_common(p, true)) return rc;
+  if (p->block_q != 128 || p->block_kv != 128) return fail(SPLASH_INVALID_ARGUMENT, "the backward schedule is 128x128");
+  if (p->num_stages < 1 || p->num_stages > kBwdStagesMax) return fail(SPLASH_INVALID_ARGUMENT, "num_stages_bwd must be in [1, 4]");
+  if (p->q_len % 128 || p->kv_len % 128) return fail(SPLASH_INVALID_ARGUMENT, "Sequence lengths must be multiples of 128");
+  if (p->sub_block != 0 && p->sub_block != 64 && p->sub_block != 128)
+    return fail(SPLASH_INVALID_ARGUMENT, "sub_block must be 0, 64 or 128");
+  if (p->head_dim != p->head_dim_v || (p->head_dim != 64 && p->head_dim != 128))
+    return fail(SPLASH_UNSUPPORTED, "the backward pass supports head_dim == head_dim_v in {64, 128}");
+  return SPLASH_OK;
+}
+
+extern "C" int splash_bwd_delta(const void* o, const void* d_out, float* delta, int64_t rows, int32_t head_dim_v,
+                                int32_t dtype, void* stream) {
+  return launch_delta(o, d_out, delta, rows, head_dim_v, dtype, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int splash_bwd_dq(const SplashParams* p, void* stream) {
+  if (int rc = check_bwd(p)) return rc;
+  if (!p->dq) return fail(SPLASH_INVALID_ARGUMENT, "dq is null");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // The requested sub-block is a preference: 128 keys per step when it fits in shared
+  // memory, else 64.
+  const bool want128 = p->sub_block != 64;
+  if (p->head_dim == 64) {
+    if (want128 && bwd_row_smem<64, 64, 128>(*p) <= kMaxDynamicSmem) return launch_bwd_row<64, 64, 128>(*p, st);
+    return launch_bwd_row<64, 64, 64>(*p, st);
+  }
+  if (want128 && bwd_row_smem<128, 128, 128>(*p) <= kMaxDynamicSmem) return launch_bwd_row<128, 128, 128>(*p, st);
+  return launch_bwd_row<128, 128, 64>(*p, st);
+}
+
+extern "C" int splash_bwd_dkv(const SplashParams* p, void* stream) {
+  if (int rc = check_bwd(p)) return rc;
+  if (!p->dk || !p->dv) return fail(SPLASH_INVALID_ARGUMENT, "dk / dv is null");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // Tensor memory holds S^T, dP^T, P^T, dS^T, dK and dV at once: 128 q rows per step
+  // fit at head_dim 64, 64 q rows at head_dim 128.
+  if (p->head_dim == 64) {
+    if (p->sub_block == 64) return launch_bwd_col<64, 64, 64, false>(*p, st);
+    return launch_bwd_col<64, 64, 128, false>(*p, st);
+  }
+  return launch_bwd_col<128, 128, 64, false>(*p, st);
+}
+
+extern "C" int64_t splash_bwd_fused_workspace_bytes(const SplashParams* p) {
+  if (!p) return 0;
+  return static_cast<int64_t>(p->batch) * p->heads * p->q_len * p->head_dim * 4;
+}
+
+extern "C" int splash_bwd_fused(const SplashParams* p, void* stream) {
+  if (int rc = check_bwd(p)) return rc;
+  if (!p->dq || !p->dk || !p->dv || !p->dq_acc) return fail(SPLASH_INVALID_ARGUMENT, "dq, dk, dv and dq_acc must be non-null");
+  if (p->head_dim != 128) return fail(SPLASH_UNSUPPORTED, "the fused backward is compiled for head_dim 128");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  SPLASH_CUDA_CHECK(cudaMemsetAsync(p->dq_acc, 0, static_cast<size_t>(splash_bwd_fused_workspace_bytes(p)), st));
+  if (int rc = launch_bwd_col<128, 128, 64, true>(*p, st)) return rc;
+  return launch_dq_transpose_cast(p->dq_acc, p->dq, static_cast<long long>(p->batch) * p->heads, p->head_dim, p->q_len,
+                                  p->dtype, st);
 }
 
 extern "C" int splash_read_status(const int32_t* status, int32_t* host_out, void* stream) {

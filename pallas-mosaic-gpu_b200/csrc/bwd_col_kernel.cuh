@@ -1,0 +1,581 @@
+// Splash attention backward over the column (per-KV-block) schedule, sm_100a.
+//
+// One CTA owns one 128-row KV block of one KV head and walks every q block that
+// sees it, for every q head of the KV head's group, so dK and dV are complete when
+// the CTA ends: GQA/MQA heads are reduced in tensor memory, not across CTAs.
+//
+//   FUSED = false   dK, dV only (the split backward; dQ comes from bwd_row_kernel).
+//   FUSED = true    also dQ: each step's dQ^T = K^T dS^T tile is reduce-added into an
+//                   f32 accumulator laid out [batch, heads, head_dim, q_len] with a
+//                   TMA add-reduction (head_dim 128, 64 q rows per step).
+//
+// Per step (BC q rows of one q block):
+//   S^T  = K Q^T        smem x smem -> TMEM f32   [128 kv, BC]
+//   dP^T = V dO^T       smem x smem -> TMEM f32
+//   elementwise (thread = kv row, two warpgroups split the BC columns):
+//     P^T  = exp2((S^T - lse) log2e)   masked entries 0
+//     dS^T = P^T (dP^T - delta) [ (1 - tanh^2) with soft-cap ]
+//     both written to TMEM as packed 16-bit; FUSED also stages dS^T in shared memory
+//   dV  += P^T dO       TMEM x smem
+//   dK  += dS^T Q       TMEM x smem
+//   dQ^T = K^T dS^T     smem x smem (FUSED), drained by a writer warpgroup
+//
+// Behaviour follows the reference kernels (splash_attention_mgpu/backward.py:377-785,
+// backward_fused.py:64-512); the code shares nothing with them.
+#pragma once
+
+#include <stddef.h>
+
+#include "../../include/splash_sm100.h"
+#include "fwd_kernel.cuh"  // math constants
+#include "ptx.cuh"
+
+namespace splash {
+
+struct BwdArgs {
+  const int32_t* num_steps;
+  const int32_t* block_order;
+  const int32_t* block_list;
+  const int32_t* block_kind;
+  const int32_t* mask_block;
+  const int32_t* mask_desc;
+  const int32_t* seg_q;
+  const int32_t* seg_kv;
+  const float* lse;
+  const float* delta;
+  void* dq;
+  void* dk;
+  void* dv;
+  int32_t* status;
+  int32_t batch, heads, kv_heads, q_len, kv_len;
+  int32_t mask_heads, max_steps, q_blocks, kv_blocks, stages;
+  int32_t has_dense, has_seg;
+  float mask_value, soft_cap;
+};
+
+enum BwdSite : int {
+  kBSiteTmaEmpty = 21, kBSiteMmaKV, kBSiteMmaFull, kBSiteMmaP, kBSiteMmaDqFree,
+  kBSiteEwFull, kBSiteEwS, kBSiteEwDone, kBSiteEwEpi,
+  kBSiteWrReady, kBSiteWrBarA, kBSiteWrBarB,
+};
+
+template <int D, int DV, int BC, bool FUSED>
+struct ColLayout {
+  static constexpr int kRows = 128;  // kv rows per CTA
+  static constexpr int kSub = 128 / BC;
+  static constexpr int kKBytes = kRows * D * 2;
+  static constexpr int kVBytes = kRows * DV * 2;
+  static constexpr int kQStage = BC * D * 2;
+  static constexpr int kDoStage = BC * DV * 2;
+  static constexpr int kVecStage = BC * 4;          // lse, delta, q segment ids: BC words each
+  static constexpr int kMaskStage = kRows * BC;     // int8, transposed block slice
+  static constexpr int kDsStage = kRows * BC * 2;   // FUSED: dS^T as an MMA operand
+  static constexpr int kDqStage = 128 * BC * 4;     // FUSED: dQ^T tile, f32
+  // Tensor memory columns.
+  static constexpr int kColS = 0, kColDp = BC, kColP = 2 * BC, kColDs = 2 * BC + BC / 2;
+  static constexpr int kColDk = 3 * BC, kColDv = 3 * BC + D, kColDq = 3 * BC + D + DV;
+  static constexpr int kTmemUsed = 3 * BC + D + DV + (FUSED ? BC : 0);
+  static constexpr int kTmemCols = kTmemUsed <= 256 ? 256 : 512;
+  static constexpr int kEwThreads = 256;
+  static constexpr int kThreads = kEwThreads + (FUSED ? 128 : 0) + 128;
+  static_assert(kTmemUsed <= 512, "tensor memory budget");
+
+  __host__ __device__ static size_t smem_bytes(int stages, bool dense, bool seg) {
+    size_t b = 1024;
+    b += kKBytes + kVBytes;
+    b += static_cast<size_t>(stages) * (kQStage + kDoStage + 2 * kVecStage);
+    if (seg) b += static_cast<size_t>(stages) * kVecStage;
+    if (dense) b += static_cast<size_t>(stages) * kMaskStage;
+    if (FUSED) b += 2 * kDsStage + kDqStage;
+    b += 1024;
+    return b;
+  }
+};
+
+constexpr int kBwdMaxStages = 4;
+
+struct ColBarriers {
+  uint64_t kv_full;
+  uint64_t full[kBwdMaxStages], empty[kBwdMaxStages];
+  uint64_t s_ready, p_ready, acc_done;
+  uint64_t dq_ready, dq_free, wr_a, wr_b;
+  uint64_t epi[2];
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+  uint32_t dead;
+};
+
+#define SPLASH_CBAR(field, idx) \
+  (bars_u32 + static_cast<uint32_t>(offsetof(ColBarriers, field)) + 8u * static_cast<uint32_t>(idx))
+
+// Enumerates the steps of one CTA: q heads of the group x visited q blocks x sub-blocks.
+template <int SUB>
+struct ColSteps {
+  const BwdArgs* a;
+  int kj, head0, group;
+  int g, s, sb, n;
+
+  __device__ __forceinline__ int mask_head(int gg) const { return a->mask_heads > 1 ? head0 + gg : 0; }
+  __device__ __forceinline__ int steps_of(int gg) const { return a->num_steps[mask_head(gg) * a->kv_blocks + kj]; }
+  __device__ __forceinline__ void skip_empty() {
+    while (g < group && n == 0) {
+      ++g;
+      if (g < group) n = steps_of(g);
+    }
+  }
+  __device__ __forceinline__ void init(const BwdArgs* args, int kj_, int head0_, int group_) {
+    a = args; kj = kj_; head0 = head0_; group = group_;
+    g = 0; s = 0; sb = 0;
+    n = steps_of(0);
+    skip_empty();
+  }
+  __device__ __forceinline__ bool valid() const { return g < group; }
+  __device__ __forceinline__ void next() {
+    if (++sb == SUB) {
+      sb = 0;
+      if (++s == n) {
+        s = 0;
+        ++g;
+        if (g < group) n = steps_of(g);
+        skip_empty();
+      }
+    }
+  }
+  __device__ __forceinline__ int head() const { return head0 + g; }
+  __device__ __forceinline__ int off() const { return (mask_head(g) * a->kv_blocks + kj) * a->max_steps + s; }
+  __device__ __forceinline__ int total() const {
+    int t = 0;
+    for (int gg = 0; gg < group; ++gg) t += steps_of(gg);
+    return t * SUB;
+  }
+};
+
+template <int D, int DV, int BC, bool FUSED, bool BF16>
+__global__ void __launch_bounds__(ColLayout<D, DV, BC, FUSED>::kThreads, 1)
+splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                      const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+                      const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv,
+                      const __grid_constant__ CUtensorMap tm_mask, const __grid_constant__ CUtensorMap tm_dqacc,
+                      const BwdArgs a) {
+  using L = ColLayout<D, DV, BC, FUSED>;
+  constexpr int kRows = 128;
+  constexpr int kSub = L::kSub;
+  constexpr int kEwWarps = 8;
+  constexpr int kWriterWarp0 = kEwWarps;                       // FUSED only
+  constexpr int kProducerWarp0 = kEwWarps + (FUSED ? 4 : 0);
+  constexpr int kHalf = BC / 2;                                // columns per elementwise warpgroup
+
+  extern __shared__ uint8_t smem_raw[];
+  const int stages = a.stages;
+  const uint32_t k_u32 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t v_u32 = k_u32 + L::kKBytes;
+  const uint32_t q_u32 = v_u32 + L::kVBytes;
+  const uint32_t do_u32 = q_u32 + stages * L::kQStage;
+  const uint32_t ds_u32 = do_u32 + stages * L::kDoStage;              // FUSED: 2 x dS^T
+  const uint32_t dqs_u32 = ds_u32 + (FUSED ? 2 * L::kDsStage : 0);    // FUSED: dQ^T staging
+  const uint32_t mask_u32 = dqs_u32 + (FUSED ? L::kDqStage : 0);
+  const uint32_t lse_u32 = mask_u32 + (a.has_dense ? stages * L::kMaskStage : 0);
+  const uint32_t delta_u32 = lse_u32 + stages * L::kVecStage;
+  const uint32_t segq_u32 = delta_u32 + stages * L::kVecStage;
+  const uint32_t bars_u32 = (segq_u32 + (a.has_seg ? stages * L::kVecStage : 0) + 15u) & ~15u;
+  const uint32_t abort_u32 = bars_u32 + static_cast<uint32_t>(offsetof(ColBarriers, abort_flag));
+  const uint32_t dead_u32 = bars_u32 + static_cast<uint32_t>(offsetof(ColBarriers, dead));
+  const uint32_t tmem_slot_u32 = bars_u32 + static_cast<uint32_t>(offsetof(ColBarriers, tmem_base));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // ---- which KV block ----------------------------------------------------------
+  const int group = a.heads / a.kv_heads;
+  const int hb_count = a.kv_heads * a.batch;
+  const int order_idx = blockIdx.x / hb_count;
+  const int hb = blockIdx.x - order_idx * hb_count;
+  const int kvh = hb % a.kv_heads;
+  const int b = hb / a.kv_heads;
+  const int head0 = kvh * group;
+  const int mh0 = a.mask_heads > 1 ? head0 : 0;
+  const int kj = a.block_order[mh0 * a.kv_blocks + order_idx];
+  const int kv_row0 = (b * a.kv_heads + kvh) * a.kv_len + kj * kRows;  // row in the [B*KVH*Skv, D] view
+
+  ColSteps<kSub> it;
+  it.init(&a, kj, head0, group);
+  const int total = it.total();
+
+  if (threadIdx.x == 0) {
+    sts32(abort_u32, 0);
+    sts32(dead_u32, a.status[0] != 0);
+    mbar_init(SPLASH_CBAR(kv_full, 0), 1);
+    for (int i = 0; i < stages; ++i) {
+      mbar_init(SPLASH_CBAR(full, i), 1);
+      mbar_init(SPLASH_CBAR(empty, i), 1 + kEwWarps);
+    }
+    mbar_init(SPLASH_CBAR(s_ready, 0), 1);
+    mbar_init(SPLASH_CBAR(p_ready, 0), L::kEwThreads);
+    mbar_init(SPLASH_CBAR(acc_done, 0), 1);
+    mbar_init(SPLASH_CBAR(dq_ready, 0), 1);
+    mbar_init(SPLASH_CBAR(dq_free, 0), 128);
+    mbar_init(SPLASH_CBAR(wr_a, 0), 128);
+    mbar_init(SPLASH_CBAR(wr_b, 0), 128);
+    mbar_init(SPLASH_CBAR(epi, 0), 128);
+    mbar_init(SPLASH_CBAR(epi, 1), 128);
+    fence_mbar_init();
+    fence_proxy_async_smem();
+  }
+  __syncthreads();
+  if (lds32(dead_u32)) return;
+  if (warp == kProducerWarp0 + 1) {
+    tmem_alloc(tmem_slot_u32, L::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = lds32(tmem_slot_u32);
+  const WaitCtx ctx{abort_u32, a.status};
+  constexpr uint32_t kDescHi = desc_hi(1024);
+
+  if (warp >= kProducerWarp0) {
+    if (warp == kProducerWarp0 && lane == 0 && total > 0) {
+      // ------------------------------ TMA producer ------------------------------
+      prefetch_tensormap(&tm_q);
+      prefetch_tensormap(&tm_do);
+      mbar_arrive_expect_tx(SPLASH_CBAR(kv_full, 0), L::kKBytes + L::kVBytes);
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c)
+        tma_load_2d(k_u32 + c * (kRows * 128), &tm_k, c * 64, kv_row0, SPLASH_CBAR(kv_full, 0));
+#pragma unroll
+      for (int c = 0; c < DV / 64; ++c)
+        tma_load_2d(v_u32 + c * (kRows * 128), &tm_v, c * 64, kv_row0, SPLASH_CBAR(kv_full, 0));
+      int slot = 0;
+      uint32_t phase = 0;
+      for (int t = 0; it.valid(); it.next(), ++t) {
+        const int off = it.off();
+        const int qblk = a.block_list[off];
+        const int q_row = (b * a.heads + it.head()) * a.q_len + qblk * 128 + it.sb * BC;
+        if (t >= stages && !mbar_wait(SPLASH_CBAR(empty, slot), phase ^ 1, ctx, kBSiteTmaEmpty, t)) break;
+        const bool partial_dense = a.has_dense && a.block_kind[off] == SPLASH_BLOCK_PARTIAL;
+        const uint32_t bytes = L::kQStage + L::kDoStage + 2 * L::kVecStage + (a.has_seg ? L::kVecStage : 0) +
+                               (partial_dense ? L::kMaskStage : 0);
+        const uint32_t bar = SPLASH_CBAR(full, slot);
+        mbar_arrive_expect_tx(bar, bytes);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_2d(q_u32 + slot * L::kQStage + c * (BC * 128), &tm_q, c * 64, q_row, bar);
+#pragma unroll
+        for (int c = 0; c < DV / 64; ++c)
+          tma_load_2d(do_u32 + slot * L::kDoStage + c * (BC * 128), &tm_do, c * 64, q_row, bar);
+        bulk_load_1d(lse_u32 + slot * L::kVecStage, a.lse + q_row, L::kVecStage, bar);
+        bulk_load_1d(delta_u32 + slot * L::kVecStage, a.delta + q_row, L::kVecStage, bar);
+        if (a.has_seg)
+          bulk_load_1d(segq_u32 + slot * L::kVecStage,
+                       a.seg_q + static_cast<size_t>(b) * a.q_len + qblk * 128 + it.sb * BC, L::kVecStage, bar);
+        if (partial_dense)
+          tma_load_2d(mask_u32 + slot * L::kMaskStage, &tm_mask, it.sb * BC, a.mask_block[off] * 128, bar);
+        if (++slot == stages) { slot = 0; phase ^= 1; }
+      }
+    } else if (warp == kProducerWarp0 + 1 && lane == 0 && total > 0) {
+      // ------------------------------- MMA issuer -------------------------------
+      constexpr uint32_t kIdescScore = make_idesc(BF16, 128, BC, false, false);   // K Q^T, V dO^T
+      constexpr uint32_t kIdescDv = make_idesc(BF16, 128, DV, false, true);       // P^T dO
+      constexpr uint32_t kIdescDk = make_idesc(BF16, 128, D, false, true);        // dS^T Q
+      constexpr uint32_t kIdescDq = make_idesc(BF16, 128, BC, true, true);        // K^T dS^T
+      auto issue_scores = [&](int slot) {
+        const uint32_t k_lo = desc_lo(k_u32, 16), q_lo = desc_lo(q_u32 + slot * L::kQStage, 16);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          umma_ss2(tmem + L::kColS, k_lo + (((kk / 4) * (kRows * 128) + (kk % 4) * 32) >> 4), kDescHi,
+                   q_lo + (((kk / 4) * (BC * 128) + (kk % 4) * 32) >> 4), kDescHi, kIdescScore, kk > 0);
+        const uint32_t v_lo = desc_lo(v_u32, 16), do_lo = desc_lo(do_u32 + slot * L::kDoStage, 16);
+#pragma unroll
+        for (int kk = 0; kk < DV / 16; ++kk)
+          umma_ss2(tmem + L::kColDp, v_lo + (((kk / 4) * (kRows * 128) + (kk % 4) * 32) >> 4), kDescHi,
+                   do_lo + (((kk / 4) * (BC * 128) + (kk % 4) * 32) >> 4), kDescHi, kIdescScore, kk > 0);
+      };
+      bool ok = mbar_wait(SPLASH_CBAR(kv_full, 0), 0, ctx, kBSiteMmaKV, 0) &&
+                mbar_wait(SPLASH_CBAR(full, 0), 0, ctx, kBSiteMmaFull, 0);
+      if (ok) {
+        tc_fence_after();
+        issue_scores(0);
+        umma_commit(SPLASH_CBAR(s_ready, 0));
+        int slot = 0;
+        uint32_t phase = 0;
+        for (int t = 0; t < total; ++t) {
+          int slot1 = slot + 1;
+          uint32_t phase1 = phase;
+          if (slot1 == stages) { slot1 = 0; phase1 ^= 1; }
+          if (!mbar_wait(SPLASH_CBAR(p_ready, 0), t & 1, ctx, kBSiteMmaP, t)) break;
+          tc_fence_after();
+          {
+            // dV += P^T dO ; dK += dS^T Q   (B operands MN-major: boxes of 64 columns, BC rows each)
+            const uint32_t do_lo = desc_lo(do_u32 + slot * L::kDoStage, BC * 128);
+            const uint32_t q_lo = desc_lo(q_u32 + slot * L::kQStage, BC * 128);
+#pragma unroll
+            for (int kk = 0; kk < BC / 16; ++kk)
+              umma_ts2(tmem + L::kColDv, tmem + L::kColP + kk * 8, do_lo + ((kk * 2048) >> 4), kDescHi, kIdescDv,
+                       (t > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+            for (int kk = 0; kk < BC / 16; ++kk)
+              umma_ts2(tmem + L::kColDk, tmem + L::kColDs + kk * 8, q_lo + ((kk * 2048) >> 4), kDescHi, kIdescDk,
+                       (t > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(SPLASH_CBAR(empty, slot));
+          if (t + 1 < total) {
+            if (!mbar_wait(SPLASH_CBAR(full, slot1), phase1, ctx, kBSiteMmaFull, t + 1)) break;
+            tc_fence_after();
+            issue_scores(slot1);
+            umma_commit(SPLASH_CBAR(s_ready, 0));
+          }
+          if constexpr (FUSED) {
+            if (t > 0 && !mbar_wait(SPLASH_CBAR(dq_free, 0), (t - 1) & 1, ctx, kBSiteMmaDqFree, t)) break;
+            tc_fence_after();
+            // dQ^T[d, q] = sum_kv K[kv, d] dS^T[kv, q]: A = K read MN-major, B = staged dS^T MN-major.
+            const uint32_t k_lo = desc_lo(k_u32, kRows * 128);
+            const uint32_t ds_lo = desc_lo(ds_u32 + (t & 1) * L::kDsStage, kRows * 128);
+#pragma unroll
+            for (int kk = 0; kk < kRows / 16; ++kk)
+              umma_ss2(tmem + L::kColDq, k_lo + ((kk * 2048) >> 4), kDescHi, ds_lo + ((kk * 2048) >> 4), kDescHi,
+                       kIdescDq, kk > 0);
+            umma_commit(SPLASH_CBAR(dq_ready, 0));
+          }
+          slot = slot1;
+          phase = phase1;
+        }
+        umma_commit(SPLASH_CBAR(acc_done, 0));
+      }
+    }
+  } else if (FUSED && warp >= kWriterWarp0) {
+    // ================================ dQ writer ==================================
+    if constexpr (FUSED) {
+      const int wq = warp & 3;
+      const int drow = wq * 32 + lane;  // head-dim index = TMEM lane
+      const uint32_t dq_tmem = tmem + (static_cast<uint32_t>(wq * 32) << 16) + L::kColDq;
+      const bool leader = (warp == kWriterWarp0 && lane == 0);
+      int t = 0;
+      for (; it.valid(); it.next(), ++t) {
+        const int qblk = a.block_list[it.off()];
+        if (!warp_wait(SPLASH_CBAR(dq_ready, 0), t & 1, ctx, kBSiteWrReady, t)) break;
+        tc_fence_after();
+        uint32_t acc[BC];
+#pragma unroll
+        for (int c = 0; c < BC / 32; ++c) tmem_ld32(dq_tmem + c * 32, acc + c * 32);
+        tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive(SPLASH_CBAR(dq_free, 0));
+        // The previous tile's reduction must have read the staging buffer.
+        if (leader) bulk_wait_group_read<0>();
+        mbar_arrive(SPLASH_CBAR(wr_a, 0));
+        if (!warp_wait(SPLASH_CBAR(wr_a, 0), t & 1, ctx, kBSiteWrBarA, t)) break;
+#pragma unroll
+        for (int c = 0; c < BC / 4; ++c) {
+          // 32 f32 (128 bytes) per row and box; boxes of 32 q columns side by side.
+          const uint32_t box = dqs_u32 + (c / 8) * (128 * 128);
+          sts128(box + swz128(drow, c & 7), make_uint4(acc[c * 4], acc[c * 4 + 1], acc[c * 4 + 2], acc[c * 4 + 3]));
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(SPLASH_CBAR(wr_b, 0));
+        if (!warp_wait(SPLASH_CBAR(wr_b, 0), t & 1, ctx, kBSiteWrBarB, t)) break;
+        if (leader) {
+          const int x = qblk * 128 + it.sb * BC;
+          const int y = (b * a.heads + it.head()) * D;
+#pragma unroll
+          for (int c = 0; c < BC / 32; ++c) tma_reduce_add_2d(&tm_dqacc, dqs_u32 + c * (128 * 128), x + c * 32, y);
+          bulk_commit_group();
+        }
+      }
+      if (leader) bulk_wait_group<0>();
+    }
+  } else {
+    // ========================== elementwise warpgroups ===========================
+    const int w = warp >> 2;                 // which half of the BC columns
+    const int wq = warp & 3;
+    const int row = wq * 32 + lane;          // kv row inside the block
+    const int kv_pos = kj * kRows + row;
+    const uint32_t tmem_row = tmem + (static_cast<uint32_t>(wq * 32) << 16);
+    const int col0 = w * kHalf;              // first column this thread handles
+
+    if (total == 0) {
+      // No q block sees this KV block: its gradients are zero.
+      if (w == 0) {
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(a.dk) + static_cast<size_t>(kv_row0 + row) * (D * 2));
+#pragma unroll
+        for (int c = 0; c < D * 2 / 16; ++c) dst[c] = make_uint4(0, 0, 0, 0);
+      } else {
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(a.dv) + static_cast<size_t>(kv_row0 + row) * (DV * 2));
+#pragma unroll
+        for (int c = 0; c < DV * 2 / 16; ++c) dst[c] = make_uint4(0, 0, 0, 0);
+      }
+    } else {
+      const int my_seg = a.has_seg ? a.seg_kv[static_cast<size_t>(b) * a.kv_len + kv_pos] : 0;
+      const bool cap_on = a.soft_cap > 0.f;
+      const float cap = a.soft_cap, inv_cap = cap_on ? 1.f / a.soft_cap : 0.f;
+      bool alive = true;
+      int slot = 0;
+      uint32_t phase = 0;
+      int cur_mh = -1;
+      int band_lo = -(1 << 30), band_hi = (1 << 30);  // allowed range of kv_pos - q_pos for this kv row
+
+      for (int t = 0; it.valid(); it.next(), ++t) {
+        const int off = it.off();
+        const int qblk = a.block_list[off];
+        const bool partial = a.block_kind[off] == SPLASH_BLOCK_PARTIAL;
+        if (a.mask_desc && it.mask_head(it.g) != cur_mh) {
+          cur_mh = it.mask_head(it.g);
+          band_lo = a.mask_desc[cur_mh * 4 + 0];
+          band_hi = a.mask_desc[cur_mh * 4 + 1];
+          const int chunk = a.mask_desc[cur_mh * 4 + 2];
+          if (chunk > 0) {
+            // q must share the kv row's chunk: start <= q_pos <= start + chunk - 1.
+            const int start = (kv_pos / chunk) * chunk;
+            band_lo = max(band_lo, kv_pos - (start + chunk - 1));
+            band_hi = min(band_hi, kv_pos - start);
+          }
+        }
+        if (!warp_wait(SPLASH_CBAR(full, slot), phase, ctx, kBSiteEwFull, t)) { alive = false; break; }
+        if (!warp_wait(SPLASH_CBAR(s_ready, 0), t & 1, ctx, kBSiteEwS, t)) { alive = false; break; }
+        tc_fence_after();
+        const int q0 = qblk * 128 + it.sb * BC + col0;  // sequence position of this thread's first column
+#pragma unroll
+        for (int c = 0; c < kHalf / 32; ++c) {
+          uint32_t sraw[32], dpraw[32];
+          tmem_ld32(tmem_row + L::kColS + col0 + c * 32, sraw);
+          tmem_ld32(tmem_row + L::kColDp + col0 + c * 32, dpraw);
+          tmem_wait_ld();
+          uint32_t vis = 0xffffffffu;  // bit i: column i of this chunk is visible
+          if (partial && !a.has_dense) {
+            const int d0 = kv_pos - (q0 + c * 32);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int d = d0 - i;
+              if (d < band_lo || d > band_hi) vis &= ~(1u << i);
+            }
+          }
+          if (partial && a.has_dense) {
+            // Transposed block slice: rows = kv, BC bytes per row, TMA-swizzled.
+#pragma unroll
+            for (int g = 0; g < 2; ++g) {
+              uint32_t o = row * BC + col0 + c * 32 + g * 16;
+              o ^= ((o >> 7) & (BC == 128 ? 7u : 3u)) << 4;
+              const uint4 wd = lds128(mask_u32 + slot * L::kMaskStage + o);
+              const uint32_t ww[4] = {wd.x, wd.y, wd.z, wd.w};
+#pragma unroll
+              for (int e = 0; e < 16; ++e)
+                if (((ww[e >> 2] >> ((e & 3) * 8)) & 0xff) == 0) vis &= ~(1u << (g * 16 + e));
+            }
+          }
+          if (a.has_seg) {
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              const uint4 sg = lds128(segq_u32 + slot * L::kVecStage + (col0 + c * 32 + g * 4) * 4);
+              if (static_cast<int>(sg.x) != my_seg) vis &= ~(1u << (g * 4 + 0));
+              if (static_cast<int>(sg.y) != my_seg) vis &= ~(1u << (g * 4 + 1));
+              if (static_cast<int>(sg.z) != my_seg) vis &= ~(1u << (g * 4 + 2));
+              if (static_cast<int>(sg.w) != my_seg) vis &= ~(1u << (g * 4 + 3));
+            }
+          }
+          uint32_t ppk[16], dspk[16];
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            const uint4 lw = lds128(lse_u32 + slot * L::kVecStage + (col0 + c * 32 + g * 4) * 4);
+            const uint4 dw = lds128(delta_u32 + slot * L::kVecStage + (col0 + c * 32 + g * 4) * 4);
+            const float lses[4] = {__uint_as_float(lw.x), __uint_as_float(lw.y), __uint_as_float(lw.z), __uint_as_float(lw.w)};
+            const float dels[4] = {__uint_as_float(dw.x), __uint_as_float(dw.y), __uint_as_float(dw.z), __uint_as_float(dw.w)};
+            float pv[4], dsv[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int i = g * 4 + e;
+              float sval = __uint_as_float(sraw[i]);
+              float tanh_v = 0.f;
+              if (cap_on) {
+                tanh_v = tanh_approx(sval * inv_cap);
+                sval = cap * tanh_v;
+              }
+              // Rows that saw no key carry lse = mask_value; they contribute nothing.
+              const bool on = ((vis >> i) & 1u) && lses[e] != a.mask_value;
+              const float p = on ? ex2_approx((sval - lses[e]) * kLog2e) : 0.f;
+              float ds = p * (__uint_as_float(dpraw[i]) - dels[e]);
+              if (cap_on) ds *= (1.f - tanh_v * tanh_v);
+              pv[e] = p;
+              dsv[e] = ds;
+            }
+            ppk[g * 2] = pack2<BF16>(pv[0], pv[1]);
+            ppk[g * 2 + 1] = pack2<BF16>(pv[2], pv[3]);
+            dspk[g * 2] = pack2<BF16>(dsv[0], dsv[1]);
+            dspk[g * 2 + 1] = pack2<BF16>(dsv[2], dsv[3]);
+          }
+          tmem_st16(tmem_row + L::kColP + (col0 + c * 32) / 2, ppk);
+          tmem_st16(tmem_row + L::kColDs + (col0 + c * 32) / 2, dspk);
+          if constexpr (FUSED) {
+            // dS^T staged as [kv row][64 q], 128 bytes per row, 128-byte swizzle.
+            const uint32_t stage = ds_u32 + (t & 1) * L::kDsStage;
+            const int chunk0 = (col0 + c * 32) / 8;  // 16-byte chunk index of this thread's first column
+#pragma unroll
+            for (int g = 0; g < 4; ++g)
+              sts128(stage + swz128(row, chunk0 + g),
+                     make_uint4(dspk[g * 4], dspk[g * 4 + 1], dspk[g * 4 + 2], dspk[g * 4 + 3]));
+          }
+        }
+        // The slot's vectors and mask slice have been read.
+        __syncwarp();
+        if (lane == 0) mbar_arrive(SPLASH_CBAR(empty, slot));
+        tmem_wait_st();
+        if constexpr (FUSED) fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(SPLASH_CBAR(p_ready, 0));
+        if (++slot == stages) { slot = 0; phase ^= 1; }
+      }
+
+      // ---- epilogue: dK by warpgroup 0, dV by warpgroup 1 ---------------------------
+      if (alive) alive = warp_wait(SPLASH_CBAR(acc_done, 0), 0, ctx, kBSiteEwDone, total);
+      if (alive) {
+        tc_fence_after();
+        const uint32_t stage = w == 0 ? k_u32 : v_u32;  // K / V tiles are dead once every MMA has finished
+        const uint32_t acc_tmem = tmem_row + (w == 0 ? L::kColDk : L::kColDv);
+        constexpr int kCols = D;  // D == DV for every compiled configuration
+#pragma unroll
+        for (int c = 0; c < kCols / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld32(acc_tmem + c * 32, o);
+          tmem_wait_ld();
+          const uint32_t box = stage + (c / 2) * (kRows * 128);
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 wv;
+            wv.x = pack2<BF16>(__uint_as_float(o[g * 8 + 0]), __uint_as_float(o[g * 8 + 1]));
+            wv.y = pack2<BF16>(__uint_as_float(o[g * 8 + 2]), __uint_as_float(o[g * 8 + 3]));
+            wv.z = pack2<BF16>(__uint_as_float(o[g * 8 + 4]), __uint_as_float(o[g * 8 + 5]));
+            wv.w = pack2<BF16>(__uint_as_float(o[g * 8 + 6]), __uint_as_float(o[g * 8 + 7]));
+            sts128(box + swz128(row, (c & 1) * 4 + g), wv);
+          }
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(SPLASH_CBAR(epi, w));
+        if (row == 0) {
+          if (mbar_wait(SPLASH_CBAR(epi, w), 0, ctx, kBSiteEwEpi, total)) {
+#pragma unroll
+            for (int c = 0; c < kCols / 64; ++c)
+              tma_store_2d(w == 0 ? &tm_dk : &tm_dv, stage + c * (kRows * 128), c * 64, kv_row0);
+            bulk_commit_group();
+            bulk_wait_group<0>();
+          }
+        }
+      }
+    }
+  }
+
+  // ---- teardown ---------------------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (lds32(abort_u32)) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000) {}
+  }
+  if (warp == kProducerWarp0 + 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem, L::kTmemCols);
+  }
+}
+
+#undef SPLASH_CBAR
+
+}  // namespace splash

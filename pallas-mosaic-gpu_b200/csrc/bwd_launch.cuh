@@ -1,0 +1,143 @@
+// Host launchers for the backward kernel templates.
+#pragma once
+
+#include "bwd_col_kernel.cuh"
+#include "bwd_row_kernel.cuh"
+#include "host_common.cuh"
+
+namespace splash {
+
+inline void fill_bwd_args(BwdArgs& a, const SplashParams& p, bool dense, bool seg) {
+  a.num_steps = p.num_steps;
+  a.block_order = p.block_order;
+  a.block_list = p.block_list;
+  a.block_kind = p.block_kind;
+  a.mask_block = p.mask_block;
+  a.mask_desc = p.mask_desc;
+  a.seg_q = p.seg_q;
+  a.seg_kv = p.seg_kv;
+  a.lse = p.lse;
+  a.delta = p.delta;
+  a.dq = p.dq;
+  a.dk = p.dk;
+  a.dv = p.dv;
+  a.status = p.status;
+  a.batch = p.batch;
+  a.heads = p.heads;
+  a.kv_heads = p.kv_heads;
+  a.q_len = p.q_len;
+  a.kv_len = p.kv_len;
+  a.mask_heads = p.mask_heads;
+  a.max_steps = p.max_steps;
+  a.q_blocks = p.q_len / 128;
+  a.kv_blocks = p.kv_len / 128;
+  a.stages = p.num_stages;
+  a.has_dense = dense;
+  a.has_seg = seg;
+  a.mask_value = p.mask_value;
+  a.soft_cap = p.soft_cap;
+}
+
+template <int D, int DV, int BC, bool FUSED, bool BF16>
+int launch_bwd_col_typed(const SplashParams& p, cudaStream_t stream) {
+  using L = ColLayout<D, DV, BC, FUSED>;
+  const bool dense = p.partial_blocks != nullptr;
+  const bool seg = p.seg_q != nullptr;
+  const size_t smem = L::smem_bytes(p.num_stages, dense, seg);
+  if (smem > kMaxDynamicSmem) {
+    char d[96];
+    snprintf(d, sizeof d, "%zu > %zu bytes; reduce num_stages or the sub-block sizes", smem, kMaxDynamicSmem);
+    return fail(SPLASH_BUDGET_EXCEEDED, "shared memory budget exceeded", d);
+  }
+  const CUtensorMapDataType dt = tmap_dtype(p.dtype);
+  const uint64_t q_rows = static_cast<uint64_t>(p.batch) * p.heads * p.q_len;
+  const uint64_t kv_rows = static_cast<uint64_t>(p.batch) * p.kv_heads * p.kv_len;
+  CUtensorMap tm_q, tm_k, tm_v, tm_do, tm_dk, tm_dv, tm_mask, tm_dqacc;
+  memset(&tm_mask, 0, sizeof tm_mask);
+  memset(&tm_dqacc, 0, sizeof tm_dqacc);
+  int rc;
+  if ((rc = make_tmap_2d(&tm_q, p.q, dt, 2, q_rows, D, BC, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  if ((rc = make_tmap_2d(&tm_do, p.d_out, dt, 2, q_rows, DV, BC, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  if ((rc = make_tmap_2d(&tm_k, p.k, dt, 2, kv_rows, D, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  if ((rc = make_tmap_2d(&tm_v, p.v, dt, 2, kv_rows, DV, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  if ((rc = make_tmap_2d(&tm_dk, p.dk, dt, 2, kv_rows, D, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  if ((rc = make_tmap_2d(&tm_dv, p.dv, dt, 2, kv_rows, DV, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  if (dense) {
+    const uint64_t mrows = static_cast<uint64_t>(p.num_partial_blocks) * 128;
+    if ((rc = make_tmap_2d(&tm_mask, p.partial_blocks, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, mrows, 128, 128, BC,
+                           BC == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B)))
+      return rc;
+  }
+  if (FUSED) {
+    // f32 accumulator viewed as [batch * heads * head_dim, q_len]; tiles of 32 q columns.
+    const uint64_t acc_rows = static_cast<uint64_t>(p.batch) * p.heads * D;
+    if ((rc = make_tmap_2d(&tm_dqacc, p.dq_acc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, acc_rows, p.q_len, 128, 32,
+                           CU_TENSOR_MAP_SWIZZLE_128B)))
+      return rc;
+  }
+  BwdArgs a;
+  fill_bwd_args(a, p, dense, seg);
+  auto kernel = splash_bwd_col_kernel<D, DV, BC, FUSED, BF16>;
+  if ((rc = opt_in_smem(kernel, smem))) return rc;
+  const unsigned grid = static_cast<unsigned>(a.kv_blocks) * p.kv_heads * p.batch;
+  kernel<<<grid, L::kThreads, smem, stream>>>(tm_q, tm_k, tm_v, tm_do, tm_dk, tm_dv, tm_mask, tm_dqacc, a);
+  SPLASH_CUDA_CHECK(cudaGetLastError());
+  return SPLASH_OK;
+}
+
+template <int D, int DV, int BC, bool FUSED>
+int launch_bwd_col(const SplashParams& p, cudaStream_t stream) {
+  if (p.dtype == SPLASH_DTYPE_BF16) return launch_bwd_col_typed<D, DV, BC, FUSED, true>(p, stream);
+  return launch_bwd_col_typed<D, DV, BC, FUSED, false>(p, stream);
+}
+
+template <int D, int DV, int BC>
+size_t bwd_row_smem(const SplashParams& p) {
+  return RowLayout<D, DV, BC>::smem_bytes(p.num_stages, p.partial_blocks != nullptr, p.seg_q != nullptr);
+}
+
+template <int D, int DV, int BC, bool BF16>
+int launch_bwd_row_typed(const SplashParams& p, cudaStream_t stream) {
+  using L = RowLayout<D, DV, BC>;
+  const bool dense = p.partial_blocks != nullptr;
+  const bool seg = p.seg_q != nullptr;
+  const size_t smem = L::smem_bytes(p.num_stages, dense, seg);
+  if (smem > kMaxDynamicSmem) {
+    char d[96];
+    snprintf(d, sizeof d, "%zu > %zu bytes; reduce num_stages or the sub-block sizes", smem, kMaxDynamicSmem);
+    return fail(SPLASH_BUDGET_EXCEEDED, "shared memory budget exceeded", d);
+  }
+  const CUtensorMapDataType dt = tmap_dtype(p.dtype);
+  const uint64_t q_rows = static_cast<uint64_t>(p.batch) * p.heads * p.q_len;
+  const uint64_t kv_rows = static_cast<uint64_t>(p.batch) * p.kv_heads * p.kv_len;
+  CUtensorMap tm_q, tm_k, tm_v, tm_do, tm_dq, tm_mask;
+  memset(&tm_mask, 0, sizeof tm_mask);
+  int rc;
+  if ((rc = make_tmap_2d(&tm_q, p.q, dt, 2, q_rows, D, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  if ((rc = make_tmap_2d(&tm_do, p.d_out, dt, 2, q_rows, DV, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  if ((rc = make_tmap_2d(&tm_k, p.k, dt, 2, kv_rows, D, BC, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  if ((rc = make_tmap_2d(&tm_v, p.v, dt, 2, kv_rows, DV, BC, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  if ((rc = make_tmap_2d(&tm_dq, p.dq, dt, 2, q_rows, D, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  if (dense) {
+    const uint64_t mrows = static_cast<uint64_t>(p.num_partial_blocks) * 128;
+    if ((rc = make_tmap_2d(&tm_mask, p.partial_blocks, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, mrows, 128, 128, BC,
+                           BC == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B)))
+      return rc;
+  }
+  BwdArgs a;
+  fill_bwd_args(a, p, dense, seg);
+  auto kernel = splash_bwd_row_kernel<D, DV, BC, BF16>;
+  if ((rc = opt_in_smem(kernel, smem))) return rc;
+  const unsigned grid = static_cast<unsigned>(a.q_blocks) * p.heads * p.batch;
+  kernel<<<grid, L::kThreads, smem, stream>>>(tm_q, tm_k, tm_v, tm_do, tm_dq, tm_mask, a);
+  SPLASH_CUDA_CHECK(cudaGetLastError());
+  return SPLASH_OK;
+}
+
+template <int D, int DV, int BC>
+int launch_bwd_row(const SplashParams& p, cudaStream_t stream) {
+  if (p.dtype == SPLASH_DTYPE_BF16) return launch_bwd_row_typed<D, DV, BC, true>(p, stream);
+  return launch_bwd_row_typed<D, DV, BC, false>(p, stream);
+}
+
+}  // namespace splash

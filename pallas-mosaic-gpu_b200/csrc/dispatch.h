@@ -12,3 +12,22 @@ template <int D, int DV, int BKV, int NT>
 int launch_fwd(const SplashParams& p, cudaStream_t stream);
 
 }  // namespace splash
+
+namespace splash {
+
+template <int D, int DV, int BC, bool FUSED>
+int launch_bwd_col(const SplashParams& p, cudaStream_t stream);
+
+template <int D, int DV, int BC>
+int launch_bwd_row(const SplashParams& p, cudaStream_t stream);
+
+template <int D, int DV, int BC>
+size_t bwd_row_smem(const SplashParams& p);
+
+// delta = rowsum(dO * O); dq = cast(transpose(dq_acc)).
+int launch_delta(const void* o, const void* d_out, float* delta, long long rows, int head_dim_v, int dtype,
+                 cudaStream_t stream);
+int launch_dq_transpose_cast(const float* acc, void* dq, long long batch_heads, int head_dim, int q_len, int dtype,
+                             cudaStream_t stream);
+
+}  // namespace splash

@@ -422,7 +422,10 @@ def _forward(kernel: SplashAttentionKernel, bs: BlockSizes, q, k, v,
 
 def _use_fused_backward(q, v, bs: BlockSizes, has_dense, has_segments) -> bool:
   head_dim = q.shape[-1]
-  use = head_dim == 128 or os.environ.get("SPLASH_BWD_FUSED_D64") == "1"
+  # The fused kernel is compiled for head_dim 128 only; head_dim 64 always takes
+  # the split kernels (the reference makes the fused path opt-in there because it
+  # is slower, `splash_attention.py:299-301`).
+  use = head_dim == 128
   return bool(
       use and cfg.fused_supported(head_dim, v.shape[-1])
       and cfg.fused_fits(head_dim=head_dim, num_stages=bs.num_stages_bwd,

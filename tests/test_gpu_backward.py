@@ -1,0 +1,145 @@
+"""Backward kernels on a B200 through the public API (torch.autograd), against the
+CPU oracle's analytic gradients.
+
+Case lists replay the reference's gradient tiers (tests/test_splash_attention_mgpu.py:
+397-457 split kernels, 563-589 fused head_dim 128, 492-521 ping-pong forward + backward
+and tiling independence) at s = 2048; the bar is the reference's:
+max|g - r| / max|r| < 2e-2 per tensor.
+"""
+
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import splash_attention_mgpu as sa
+from oracle import dense_attention as oracle
+
+from common import build_mask, inputs, segments
+
+pytestmark = pytest.mark.gpu
+
+_id = lambda kw: ",".join(f"{k}={v}" for k, v in kw.items()) or "default"
+
+
+def _check_grads(mask_name, *, s=2048, b=None, h=2, kvh=None, d=64, mqa=False, segs=False, cap=None,
+                 block_sizes=sa.BlockSizes(), multi_head_mask=False, dtype=torch.bfloat16):
+  kvh = kvh or h
+  mask, dense = build_mask(mask_name, s, h, multi_head_mask)
+  make = sa.make_splash_mqa if mqa else sa.make_splash_mha
+  kernel = make(mask, block_sizes=block_sizes, attn_logits_soft_cap=cap)
+  q, k, v = inputs(b, h, kvh, s, d, d, dtype, mqa, device="cuda:0")
+  w = torch.randn(q.shape, generator=torch.Generator().manual_seed(7)).to("cuda:0")
+  seg = segments(s, "cuda:0") if segs else None
+  qg, kg, vg = (x.clone().requires_grad_(True) for x in (q, k, v))
+  out = kernel(qg, kg, vg, seg)
+  (out.float() * w).sum().backward()
+  sa.check_device_status()
+  want = oracle.attention_backward(dense, q, k, v, w, seg, is_mqa=mqa, attn_logits_soft_cap=cap)
+  for name, g, r in zip("qkv", (qg.grad, kg.grad, vg.grad), want):
+    assert g.shape == getattr(locals()[name], "shape"), name
+    g = g.float().cpu().numpy()
+    rel = np.abs(g - r).max() / np.abs(r).max()
+    assert rel < 2e-2, f"d{name}: relative error {rel}"
+    mean_rel = np.abs(g - r).mean() / np.abs(r).mean()
+    assert mean_rel < 1e-2, f"d{name}: mean relative error {mean_rel}"
+
+
+GRAD_CASES = [
+    dict(mask_name="full"),
+    dict(mask_name="causal"),
+    dict(mask_name="local", segs=True),
+    dict(mask_name="chunked"),
+    dict(mask_name="dense"),
+    dict(mask_name="dense", segs=True),
+    dict(mask_name="causal", cap=5.0),
+    dict(mask_name="causal", h=4, kvh=2),
+    dict(mask_name="causal", mqa=True, h=3),
+    dict(mask_name="causal", b=2),
+    dict(mask_name="causal", dtype=torch.float16),
+    dict(mask_name="causal", multi_head_mask=True, h=3),
+    dict(mask_name="causal", block_sizes=sa.BlockSizes(block_kv_dq=128, block_q_dkv=64, num_stages_bwd=1)),
+    dict(mask_name="dense", block_sizes=sa.BlockSizes(block_kv_dq=64, block_q_dkv=128, num_stages_bwd=3)),
+]
+
+
+@pytest.mark.parametrize("kwargs", GRAD_CASES, ids=_id)
+def test_gpu_grads(kwargs):
+  kwargs = dict(kwargs)
+  _check_grads(kwargs.pop("mask_name"), **kwargs)
+
+
+GRAD_CASES_D128 = [
+    dict(mask_name="full", d=128),
+    dict(mask_name="causal", d=128),
+    dict(mask_name="local", d=128, segs=True),
+    dict(mask_name="chunked", d=128),
+    dict(mask_name="dense", d=128),
+    dict(mask_name="dense", d=128, segs=True),
+    dict(mask_name="causal", d=128, cap=5.0),
+    dict(mask_name="causal", d=128, h=4, kvh=2),
+    dict(mask_name="causal", d=128, mqa=True, h=3),
+    dict(mask_name="causal", d=128, b=2),
+    dict(mask_name="causal", d=128, multi_head_mask=True, h=3),
+    dict(mask_name="causal", d=128, dtype=torch.float16),
+]
+
+
+@pytest.mark.parametrize("kwargs", GRAD_CASES_D128, ids=_id)
+def test_gpu_grads_fused(kwargs):
+  kwargs = dict(kwargs)
+  _check_grads(kwargs.pop("mask_name"), **kwargs)
+
+
+@pytest.mark.parametrize("kwargs", GRAD_CASES_D128, ids=_id)
+def test_gpu_grads_split_d128(kwargs, monkeypatch):
+  # SPLASH_BWD_FUSED=0 routes head_dim 128 through the dQ + dK/dV kernels.
+  monkeypatch.setenv("SPLASH_BWD_FUSED", "0")
+  kwargs = dict(kwargs)
+  _check_grads(kwargs.pop("mask_name"), **kwargs)
+
+
+@pytest.mark.parametrize("kwargs", [dict(mask_name="full"), dict(mask_name="causal"), dict(mask_name="local"),
+                                    dict(mask_name="chunked")], ids=_id)
+def test_gpu_pingpong_grads(kwargs):
+  kwargs = dict(kwargs)
+  _check_grads(kwargs.pop("mask_name"), block_sizes=sa.BlockSizes(block_q=256), **kwargs)
+
+
+@pytest.mark.parametrize("block_sizes", [sa.BlockSizes(block_kv=64), sa.BlockSizes(block_q=256, block_kv=64)],
+                         ids=["bkv64", "pingpong-bkv64"])
+def test_gpu_grads_independent_of_forward_tiling(block_sizes):
+  _check_grads("dense", block_sizes=block_sizes)
+
+
+def test_empty_columns_get_zero_gradients():
+  s = 512
+  dense = np.zeros((s, s), bool)
+  dense[:, :256] = True  # the last two KV blocks are seen by nobody
+  kernel = sa.make_splash_mha(sa.NumpyMask(dense))
+  for d in (64, 128):
+    q, k, v = inputs(None, 2, 2, s, d, d, torch.bfloat16, False, device="cuda:0")
+    qg, kg, vg = (x.clone().requires_grad_(True) for x in (q, k, v))
+    kernel(qg, kg, vg).float().sum().backward()
+    sa.check_device_status()
+    assert torch.all(kg.grad[:, 256:] == 0) and torch.all(vg.grad[:, 256:] == 0)
+    want = oracle.attention_backward(dense[None], q, k, v, torch.ones(q.shape))
+    for g, r in zip((qg.grad, kg.grad, vg.grad), want):
+      assert np.abs(g.float().cpu().numpy() - r).max() / max(np.abs(r).max(), 1e-6) < 2e-2
+
+
+def test_delta_prepass_matches_torch():
+  import ctypes
+  from splash_attention_mgpu import _ffi
+  lib = _ffi.load()
+  for dtype, code in ((torch.bfloat16, _ffi.DTYPE_BF16), (torch.float16, _ffi.DTYPE_F16)):
+    for dv in (64, 128, 192):
+      g = torch.Generator().manual_seed(dv)
+      o = torch.randn(1000, dv, generator=g).to(dtype).cuda()
+      do = torch.randn(1000, dv, generator=g).to(dtype).cuda()
+      delta = torch.empty(1000, dtype=torch.float32, device="cuda")
+      _ffi.check(lib.splash_bwd_delta(o.data_ptr(), do.data_ptr(), delta.data_ptr(), 1000, dv, code,
+                                      torch.cuda.current_stream().cuda_stream), "delta")
+      want = (o.float() * do.float()).sum(-1)
+      np.testing.assert_allclose(delta.cpu().numpy(), want.cpu().numpy(), atol=1e-3, rtol=1e-4)
