@@ -121,6 +121,32 @@ int splash_bwd_fused(const SplashParams* p, void* stream);
 /* Bytes of `dq_acc` scratch splash_bwd_fused needs for these shapes. */
 int64_t splash_bwd_fused_workspace_bytes(const SplashParams* p);
 
+/* Size of the scratch built into the library for splash_bwd_fused_static. */
+#define SPLASH_STATIC_DQ_ACC_BYTES (16u << 20)
+
+/* splash_bwd_fused without caller scratch and without any allocation.  (No counterpart
+ * in the reference: there the f32 dQ accumulator is an ordinary XLA buffer.)
+ *
+ * Who needs it: code that runs where device allocation is off limits -- the execute
+ * callback of another runtime (an XLA custom call, an inference-server plugin's
+ * enqueue hook), or a process whose memory pool is sealed after start-up.  Calling
+ * cudaMalloc there can stall the whole device, bypasses the host runtime's memory
+ * accounting, or is simply forbidden, and such callers often have no spare workspace
+ * to hand over either.
+ *
+ * The dQ accumulator is a fixed SPLASH_STATIC_DQ_ACC_BYTES (16 MiB) array inside the
+ * library image; every GPU that loads the library carries it until the process exits.
+ * `p->dq_acc` is ignored; all other fields are as for splash_bwd_fused.  Shapes with
+ * batch * heads * q_len * head_dim * 4 > SPLASH_STATIC_DQ_ACC_BYTES are refused with
+ * SPLASH_BUDGET_EXCEEDED.  The call performs no cudaMalloc / cudaFree and no allocating
+ * library call.  The first call on each device looks up the array's device address
+ * (cudaGetSymbolAddress); make that first call outside any stream capture.
+ *
+ * All calls share the one array: it is cleared at the start of each call, and two calls
+ * whose GPU work overlaps (different streams, no ordering between them) race on it --
+ * serialise them. */
+int splash_bwd_fused_static(const SplashParams* p, void* stream);
+
 /* Copies the 4-int status word to the host after synchronising `stream`; returns
  * SPLASH_OK, SPLASH_DEVICE_TIMEOUT or SPLASH_CUDA_ERROR. `host_out` may be NULL. */
 int splash_read_status(const int32_t* status, int32_t* host_out, void* stream);

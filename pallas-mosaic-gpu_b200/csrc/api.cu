@@ -134,6 +134,50 @@ extern "C" int splash_bwd_fused(const SplashParams* p, void* stream) {
                                   p->dtype, st);
 }
 
+// ---------------------------------------------------------------------------
+// Fused backward for callers that cannot allocate
+// ---------------------------------------------------------------------------
+// The f32 dQ accumulator lives in a fixed array inside the library image instead of
+// caller-provided scratch.  In host code `g_static_dq_acc` is only a handle for the
+// symbol, not a device address; the address a kernel can use comes from
+// cudaGetSymbolAddress, looked up once per device with that device current.
+constexpr size_t kStaticDqAccBytes = SPLASH_STATIC_DQ_ACC_BYTES;
+static __device__ __align__(256) float g_static_dq_acc[kStaticDqAccBytes / sizeof(float)];
+
+static int static_dq_acc_address(float** out) {
+  constexpr int kMaxDevices = 64;
+  static float* cache[kMaxDevices] = {};
+  int dev = -1;
+  SPLASH_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(SPLASH_INVALID_ARGUMENT, "device ordinal out of range");
+  float* ptr = __atomic_load_n(&cache[dev], __ATOMIC_ACQUIRE);
+  if (!ptr) {
+    void* sym = nullptr;
+    SPLASH_CUDA_CHECK(cudaGetSymbolAddress(&sym, g_static_dq_acc));
+    if (!sym) return fail(SPLASH_CUDA_ERROR, "cudaGetSymbolAddress returned a null address");
+    ptr = static_cast<float*>(sym);
+    __atomic_store_n(&cache[dev], ptr, __ATOMIC_RELEASE);
+  }
+  *out = ptr;
+  return SPLASH_OK;
+}
+
+extern "C" int splash_bwd_fused_static(const SplashParams* p, void* stream) {
+  if (int rc = check_bwd(p)) return rc;
+  SplashParams q = *p;
+  const int64_t need = splash_bwd_fused_workspace_bytes(&q);
+  if (need <= 0 || static_cast<uint64_t>(need) > kStaticDqAccBytes) {
+    char d[160];
+    snprintf(d, sizeof d, "batch * heads * q_len * head_dim * 4 = %lld bytes, the built-in scratch holds %zu",
+             static_cast<long long>(need), kStaticDqAccBytes);
+    return fail(SPLASH_BUDGET_EXCEEDED, "problem too large for splash_bwd_fused_static", d);
+  }
+  float* acc = nullptr;
+  if (int rc = static_dq_acc_address(&acc)) return rc;
+  q.dq_acc = acc;  // whatever the caller put there is ignored
+  return splash_bwd_fused(&q, stream);
+}
+
 extern "C" int splash_read_status(const int32_t* status, int32_t* host_out, void* stream) {
   int32_t h[4] = {0, 0, 0, 0};
   cudaStream_t st = static_cast<cudaStream_t>(stream);

@@ -35,6 +35,7 @@ EXPORTED_SYMBOLS = (
     "splash_bwd_dkv",
     "splash_bwd_fused",
     "splash_bwd_fused_workspace_bytes",
+    "splash_bwd_fused_static",
     "splash_read_status",
     "splash_status_string",
     "splash_last_error",
@@ -85,7 +86,7 @@ def load():
         " or `python -c 'import __graft_entry__ as g; g.build()'`.")
   lib = ctypes.CDLL(LIB_PATH)
   for name in ("splash_fwd128", "splash_fwd256", "splash_bwd_dq",
-               "splash_bwd_dkv", "splash_bwd_fused"):
+               "splash_bwd_dkv", "splash_bwd_fused", "splash_bwd_fused_static"):
     if hasattr(lib, name):
       fn = getattr(lib, name)
       fn.argtypes = [POINTER(SplashParams), c_void_p]
