@@ -284,15 +284,17 @@ def run_ours(args):
     dk_h.copy_(kd.grad, non_blocking=True)
     dv_h.copy_(vd.grad, non_blocking=True)
 
-  e2e_step()
-  barrier()
-  e_start, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-  e_start.record()
-  for _ in range(args.steps):
+  e2e_ms = float("nan")
+  if not args.no_e2e:
     e2e_step()
-  e_end.record()
-  barrier()
-  e2e_ms = e_start.elapsed_time(e_end)
+    barrier()
+    e_start, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e_start.record()
+    for _ in range(args.steps):
+      e2e_step()
+    e_end.record()
+    barrier()
+    e2e_ms = e_start.elapsed_time(e_end)
   h2d = sum(x.numel() * x.element_size() for x in (hq, hk, hv, hdo))
   d2h = sum(x.numel() * x.element_size() for x in (out_h, dq_h, dk_h, dv_h))
 
@@ -351,6 +353,7 @@ def main():
   p.add_argument("--impl", default="ours", choices=["ours", "reference"])
   p.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
   p.add_argument("--no-cpu-baseline", action="store_true")
+  p.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (used when profiling)")
   args = p.parse_args()
   if args.impl == "reference":
     run_reference(args)

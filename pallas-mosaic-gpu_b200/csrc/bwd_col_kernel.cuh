@@ -55,7 +55,7 @@ struct BwdArgs {
 
 enum BwdSite : int {
   kBSiteTmaEmpty = 21, kBSiteMmaKV, kBSiteMmaFull, kBSiteMmaP, kBSiteMmaDqFree,
-  kBSiteEwFull, kBSiteEwS, kBSiteEwDone, kBSiteEwEpi,
+  kBSiteEwFull, kBSiteEwS, kBSiteEwPds, kBSiteEwDone, kBSiteEwEpi,
   kBSiteWrReady, kBSiteWrBarA, kBSiteWrBarB,
 };
 
@@ -97,7 +97,7 @@ constexpr int kBwdMaxStages = 4;
 struct ColBarriers {
   uint64_t kv_full;
   uint64_t full[kBwdMaxStages], empty[kBwdMaxStages];
-  uint64_t s_ready, p_ready, acc_done;
+  uint64_t s_ready, p_ready, pds_free, acc_done;
   uint64_t dq_ready, dq_free, wr_a, wr_b;
   uint64_t epi[2];
   uint32_t tmem_base;
@@ -211,6 +211,7 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     }
     mbar_init(SPLASH_CBAR(s_ready, 0), 1);
     mbar_init(SPLASH_CBAR(p_ready, 0), L::kEwThreads);
+    mbar_init(SPLASH_CBAR(pds_free, 0), 1);
     mbar_init(SPLASH_CBAR(acc_done, 0), 1);
     mbar_init(SPLASH_CBAR(dq_ready, 0), 1);
     mbar_init(SPLASH_CBAR(dq_free, 0), 128);
@@ -305,6 +306,19 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           if (slot1 == stages) { slot1 = 0; phase1 ^= 1; }
           if (!mbar_wait(SPLASH_CBAR(p_ready, 0), t & 1, ctx, kBSiteMmaP, t)) break;
           tc_fence_after();
+          auto issue_next_scores = [&]() -> bool {
+            if (t + 1 >= total) return true;
+            if (!mbar_wait(SPLASH_CBAR(full, slot1), phase1, ctx, kBSiteMmaFull, t + 1)) return false;
+            tc_fence_after();
+            issue_scores(slot1);
+            umma_commit(SPLASH_CBAR(s_ready, 0));
+            return true;
+          };
+          // S^T / dP^T of step t have been read, so the next scores go first: the
+          // elementwise warps start on them while dV, dK (and dQ) of step t still run.
+          // (With a single stage the next Q/dO tile only arrives after dK has released
+          // this one, so the order is the other way round.)
+          if (stages > 1 && !issue_next_scores()) break;
           {
             // dV += P^T dO ; dK += dS^T Q   (B operands MN-major: boxes of 64 columns, BC rows each)
             const uint32_t do_lo = desc_lo(do_u32 + slot * L::kDoStage, BC * 128);
@@ -319,12 +333,8 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                        (t > 0 || kk > 0) ? 1u : 0u);
           }
           umma_commit(SPLASH_CBAR(empty, slot));
-          if (t + 1 < total) {
-            if (!mbar_wait(SPLASH_CBAR(full, slot1), phase1, ctx, kBSiteMmaFull, t + 1)) break;
-            tc_fence_after();
-            issue_scores(slot1);
-            umma_commit(SPLASH_CBAR(s_ready, 0));
-          }
+          umma_commit(SPLASH_CBAR(pds_free, 0));  // P^T / dS^T of step t may be overwritten
+          if (stages == 1 && !issue_next_scores()) break;
           if constexpr (FUSED) {
             if (t > 0 && !mbar_wait(SPLASH_CBAR(dq_free, 0), (t - 1) & 1, ctx, kBSiteMmaDqFree, t)) break;
             tc_fence_after();
@@ -440,68 +450,93 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           tmem_ld32(tmem_row + L::kColS + col0 + c * 32, sraw);
           tmem_ld32(tmem_row + L::kColDp + col0 + c * 32, dpraw);
           tmem_wait_ld();
-          uint32_t vis = 0xffffffffu;  // bit i: column i of this chunk is visible
-          if (partial && !a.has_dense) {
-            const int d0 = kv_pos - (q0 + c * 32);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int d = d0 - i;
-              if (d < band_lo || d > band_hi) vis &= ~(1u << i);
-            }
-          }
-          if (partial && a.has_dense) {
-            // Transposed block slice: rows = kv, BC bytes per row, TMA-swizzled.
-#pragma unroll
-            for (int g = 0; g < 2; ++g) {
-              uint32_t o = row * BC + col0 + c * 32 + g * 16;
-              o ^= ((o >> 7) & (BC == 128 ? 7u : 3u)) << 4;
-              const uint4 wd = lds128(mask_u32 + slot * L::kMaskStage + o);
-              const uint32_t ww[4] = {wd.x, wd.y, wd.z, wd.w};
-#pragma unroll
-              for (int e = 0; e < 16; ++e)
-                if (((ww[e >> 2] >> ((e & 3) * 8)) & 0xff) == 0) vis &= ~(1u << (g * 16 + e));
-            }
-          }
-          if (a.has_seg) {
+          uint32_t ppk[16], dspk[16];
+          const uint32_t vec_off = slot * L::kVecStage + (col0 + c * 32) * 4;
+          if (!partial && !a.has_seg && !cap_on) {
+            // FULL block, no segment ids, no soft-cap: nothing to mask.  (A row whose lse
+            // is mask_value never meets a FULL block, so no guard is needed here.)
 #pragma unroll
             for (int g = 0; g < 8; ++g) {
-              const uint4 sg = lds128(segq_u32 + slot * L::kVecStage + (col0 + c * 32 + g * 4) * 4);
-              if (static_cast<int>(sg.x) != my_seg) vis &= ~(1u << (g * 4 + 0));
-              if (static_cast<int>(sg.y) != my_seg) vis &= ~(1u << (g * 4 + 1));
-              if (static_cast<int>(sg.z) != my_seg) vis &= ~(1u << (g * 4 + 2));
-              if (static_cast<int>(sg.w) != my_seg) vis &= ~(1u << (g * 4 + 3));
+              const uint4 lw = lds128(lse_u32 + vec_off + g * 16);
+              const uint4 dw = lds128(delta_u32 + vec_off + g * 16);
+              const float nl0 = __uint_as_float(lw.x) * -kLog2e, nl1 = __uint_as_float(lw.y) * -kLog2e;
+              const float nl2 = __uint_as_float(lw.z) * -kLog2e, nl3 = __uint_as_float(lw.w) * -kLog2e;
+              const float p0 = ex2_approx(fmaf(__uint_as_float(sraw[g * 4 + 0]), kLog2e, nl0));
+              const float p1 = ex2_approx(fmaf(__uint_as_float(sraw[g * 4 + 1]), kLog2e, nl1));
+              const float p2 = ex2_approx(fmaf(__uint_as_float(sraw[g * 4 + 2]), kLog2e, nl2));
+              const float p3 = ex2_approx(fmaf(__uint_as_float(sraw[g * 4 + 3]), kLog2e, nl3));
+              ppk[g * 2] = pack2<BF16>(p0, p1);
+              ppk[g * 2 + 1] = pack2<BF16>(p2, p3);
+              dspk[g * 2] = pack2<BF16>(p0 * (__uint_as_float(dpraw[g * 4 + 0]) - __uint_as_float(dw.x)),
+                                        p1 * (__uint_as_float(dpraw[g * 4 + 1]) - __uint_as_float(dw.y)));
+              dspk[g * 2 + 1] = pack2<BF16>(p2 * (__uint_as_float(dpraw[g * 4 + 2]) - __uint_as_float(dw.z)),
+                                            p3 * (__uint_as_float(dpraw[g * 4 + 3]) - __uint_as_float(dw.w)));
             }
-          }
-          uint32_t ppk[16], dspk[16];
+          } else {
+            uint32_t vis = 0xffffffffu;  // bit i: column i of this chunk is visible
+            if (partial && !a.has_dense) {
+              const int d0 = kv_pos - (q0 + c * 32);
 #pragma unroll
-          for (int g = 0; g < 8; ++g) {
-            const uint4 lw = lds128(lse_u32 + slot * L::kVecStage + (col0 + c * 32 + g * 4) * 4);
-            const uint4 dw = lds128(delta_u32 + slot * L::kVecStage + (col0 + c * 32 + g * 4) * 4);
-            const float lses[4] = {__uint_as_float(lw.x), __uint_as_float(lw.y), __uint_as_float(lw.z), __uint_as_float(lw.w)};
-            const float dels[4] = {__uint_as_float(dw.x), __uint_as_float(dw.y), __uint_as_float(dw.z), __uint_as_float(dw.w)};
-            float pv[4], dsv[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int i = g * 4 + e;
-              float sval = __uint_as_float(sraw[i]);
-              float tanh_v = 0.f;
-              if (cap_on) {
-                tanh_v = tanh_approx(sval * inv_cap);
-                sval = cap * tanh_v;
+              for (int i = 0; i < 32; ++i) {
+                const int d = d0 - i;
+                if (d < band_lo || d > band_hi) vis &= ~(1u << i);
               }
-              // Rows that saw no key carry lse = mask_value; they contribute nothing.
-              const bool on = ((vis >> i) & 1u) && lses[e] != a.mask_value;
-              const float p = on ? ex2_approx((sval - lses[e]) * kLog2e) : 0.f;
-              float ds = p * (__uint_as_float(dpraw[i]) - dels[e]);
-              if (cap_on) ds *= (1.f - tanh_v * tanh_v);
-              pv[e] = p;
-              dsv[e] = ds;
             }
-            ppk[g * 2] = pack2<BF16>(pv[0], pv[1]);
-            ppk[g * 2 + 1] = pack2<BF16>(pv[2], pv[3]);
-            dspk[g * 2] = pack2<BF16>(dsv[0], dsv[1]);
-            dspk[g * 2 + 1] = pack2<BF16>(dsv[2], dsv[3]);
+            if (partial && a.has_dense) {
+              // Transposed block slice: rows = kv, BC bytes per row, TMA-swizzled.
+#pragma unroll
+              for (int g = 0; g < 2; ++g) {
+                uint32_t o = row * BC + col0 + c * 32 + g * 16;
+                o ^= ((o >> 7) & (BC == 128 ? 7u : 3u)) << 4;
+                const uint4 wd = lds128(mask_u32 + slot * L::kMaskStage + o);
+                const uint32_t ww[4] = {wd.x, wd.y, wd.z, wd.w};
+#pragma unroll
+                for (int e = 0; e < 16; ++e)
+                  if (((ww[e >> 2] >> ((e & 3) * 8)) & 0xff) == 0) vis &= ~(1u << (g * 16 + e));
+              }
+            }
+            if (a.has_seg) {
+#pragma unroll
+              for (int g = 0; g < 8; ++g) {
+                const uint4 sg = lds128(segq_u32 + vec_off + g * 16);
+                if (static_cast<int>(sg.x) != my_seg) vis &= ~(1u << (g * 4 + 0));
+                if (static_cast<int>(sg.y) != my_seg) vis &= ~(1u << (g * 4 + 1));
+                if (static_cast<int>(sg.z) != my_seg) vis &= ~(1u << (g * 4 + 2));
+                if (static_cast<int>(sg.w) != my_seg) vis &= ~(1u << (g * 4 + 3));
+              }
+            }
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              const uint4 lw = lds128(lse_u32 + vec_off + g * 16);
+              const uint4 dw = lds128(delta_u32 + vec_off + g * 16);
+              const float lses[4] = {__uint_as_float(lw.x), __uint_as_float(lw.y), __uint_as_float(lw.z), __uint_as_float(lw.w)};
+              const float dels[4] = {__uint_as_float(dw.x), __uint_as_float(dw.y), __uint_as_float(dw.z), __uint_as_float(dw.w)};
+              float pv[4], dsv[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int i = g * 4 + e;
+                float sval = __uint_as_float(sraw[i]);
+                float tanh_v = 0.f;
+                if (cap_on) {
+                  tanh_v = tanh_approx(sval * inv_cap);
+                  sval = cap * tanh_v;
+                }
+                // Rows that saw no key carry lse = mask_value; they contribute nothing.
+                const bool on = ((vis >> i) & 1u) && lses[e] != a.mask_value;
+                const float p = on ? ex2_approx((sval - lses[e]) * kLog2e) : 0.f;
+                float ds = p * (__uint_as_float(dpraw[i]) - dels[e]);
+                if (cap_on) ds *= (1.f - tanh_v * tanh_v);
+                pv[e] = p;
+                dsv[e] = ds;
+              }
+              ppk[g * 2] = pack2<BF16>(pv[0], pv[1]);
+              ppk[g * 2 + 1] = pack2<BF16>(pv[2], pv[3]);
+              dspk[g * 2] = pack2<BF16>(dsv[0], dsv[1]);
+              dspk[g * 2 + 1] = pack2<BF16>(dsv[2], dsv[3]);
+            }
           }
+          // dV / dK of the previous step must have consumed P^T / dS^T before they are replaced.
+          if (c == 0 && t > 0 && !warp_wait(SPLASH_CBAR(pds_free, 0), (t - 1) & 1, ctx, kBSiteEwPds, t)) { alive = false; break; }
           tmem_st16(tmem_row + L::kColP + (col0 + c * 32) / 2, ppk);
           tmem_st16(tmem_row + L::kColDs + (col0 + c * 32) / 2, dspk);
           if constexpr (FUSED) {
@@ -514,6 +549,7 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                      make_uint4(dspk[g * 4], dspk[g * 4 + 1], dspk[g * 4 + 2], dspk[g * 4 + 3]));
           }
         }
+        if (!alive) break;
         // The slot's vectors and mask slice have been read.
         __syncwarp();
         if (lane == 0) mbar_arrive(SPLASH_CBAR(empty, slot));
