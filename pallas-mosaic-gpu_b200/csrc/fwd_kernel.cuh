@@ -129,7 +129,7 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const uint32_t dead_u32 = bars_u32 + static_cast<uint32_t>(offsetof(FwdBarriers, dead));
   const uint32_t tmem_slot_u32 = bars_u32 + static_cast<uint32_t>(offsetof(FwdBarriers, tmem_base));
 
-  const int warp = threadIdx.x >> 5;
+  const int warp = uniform_warp_index();
   const int lane = threadIdx.x & 31;
 
   // ---- which tile of work ---------------------------------------------------
@@ -187,19 +187,23 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   if (warp >= kSoftmaxWarps) {
     // =========================== producer warpgroup ============================
     if constexpr (NT == 2) setmaxnreg_dec<L::kProducerRegs>();
-    if (warp == kSoftmaxWarps && lane == 0 && n > 0) {
+    if (warp == kSoftmaxWarps && n > 0) {
       // ------------------------------ TMA producer ------------------------------
+      // The whole warp runs the loop (warp-uniform control flow); one elected lane
+      // issues each group of copies.
       const int kv_row0 = (b * a.kv_heads + h / (a.heads / a.kv_heads)) * a.kv_len;
-      prefetch_tensormap(&tm_q);
-      prefetch_tensormap(&tm_k);
-      prefetch_tensormap(&tm_v);
-      mbar_arrive_expect_tx(SPLASH_BAR(q_full, 0), L::kQBytes);
+      if (elect_one()) {
+        prefetch_tensormap(&tm_q);
+        prefetch_tensormap(&tm_k);
+        prefetch_tensormap(&tm_v);
+        mbar_arrive_expect_tx(SPLASH_BAR(q_full, 0), L::kQBytes);
 #pragma unroll
-      for (int t = 0; t < NT; ++t)
+        for (int t = 0; t < NT; ++t)
 #pragma unroll
-        for (int c = 0; c < D / 64; ++c)
-          tma_load_2d(q_u32 + t * (kTile * D * 2) + c * (kTile * 128), &tm_q, c * 64, q_row0 + t * kTile,
-                      SPLASH_BAR(q_full, 0));
+          for (int c = 0; c < D / 64; ++c)
+            tma_load_2d(q_u32 + t * (kTile * D * 2) + c * (kTile * 128), &tm_q, c * 64, q_row0 + t * kTile,
+                        SPLASH_BAR(q_full, 0));
+      }
       int slot = 0;
       uint32_t phase = 0;
       int j_next = a.block_list[sched_off];
@@ -207,36 +211,43 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const int j = j_next;
         if (s + 1 < n) j_next = a.block_list[sched_off + s + 1];
         const int kv_row = kv_row0 + j * BKV;
-        if (s >= stages && !mbar_wait(SPLASH_BAR(k_empty, slot), phase ^ 1, ctx, kSiteTmaKEmpty, s)) break;
-        mbar_arrive_expect_tx(SPLASH_BAR(k_full, slot), L::kKStage);
+        if (s >= stages && !warp_wait(SPLASH_BAR(k_empty, slot), phase ^ 1, ctx, kSiteTmaKEmpty, s)) break;
+        if (elect_one()) {
+          mbar_arrive_expect_tx(SPLASH_BAR(k_full, slot), L::kKStage);
 #pragma unroll
-        for (int c = 0; c < D / 64; ++c)
-          tma_load_2d(k_u32 + slot * L::kKStage + c * (BKV * 128), &tm_k, c * 64, kv_row, SPLASH_BAR(k_full, slot));
-        if (s >= stages && !mbar_wait(SPLASH_BAR(v_empty, slot), phase ^ 1, ctx, kSiteTmaVEmpty, s)) break;
-        mbar_arrive_expect_tx(SPLASH_BAR(v_full, slot), L::kVStage);
+          for (int c = 0; c < D / 64; ++c)
+            tma_load_2d(k_u32 + slot * L::kKStage + c * (BKV * 128), &tm_k, c * 64, kv_row, SPLASH_BAR(k_full, slot));
+        }
+        if (s >= stages && !warp_wait(SPLASH_BAR(v_empty, slot), phase ^ 1, ctx, kSiteTmaVEmpty, s)) break;
+        if (elect_one()) {
+          mbar_arrive_expect_tx(SPLASH_BAR(v_full, slot), L::kVStage);
 #pragma unroll
-        for (int c = 0; c < DV / 64; ++c)
-          tma_load_2d(v_u32 + slot * L::kVStage + c * (BKV * 128), &tm_v, c * 64, kv_row, SPLASH_BAR(v_full, slot));
+          for (int c = 0; c < DV / 64; ++c)
+            tma_load_2d(v_u32 + slot * L::kVStage + c * (BKV * 128), &tm_v, c * 64, kv_row, SPLASH_BAR(v_full, slot));
+        }
         if (has_aux) {
-          if (s >= stages && !mbar_wait(SPLASH_BAR(aux_empty, slot), phase ^ 1, ctx, kSiteTmaAuxEmpty, s)) break;
+          if (s >= stages && !warp_wait(SPLASH_BAR(aux_empty, slot), phase ^ 1, ctx, kSiteTmaAuxEmpty, s)) break;
           const bool partial_dense = a.has_dense && a.block_kind[sched_off + s] == SPLASH_BLOCK_PARTIAL;
           const uint32_t bytes = (a.has_seg ? L::kSegStage : 0) + (partial_dense ? L::kMaskStage : 0);
-          mbar_arrive_expect_tx(SPLASH_BAR(aux_full, slot), bytes);
-          if (a.has_seg)
-            bulk_load_1d(seg_u32 + slot * L::kSegStage, a.seg_kv + static_cast<size_t>(b) * a.kv_len + j * BKV,
-                         L::kSegStage, SPLASH_BAR(aux_full, slot));
-          if (partial_dense) {
-            const int mrow = a.mask_block[sched_off + s] * kBq;
+          const int mrow = partial_dense ? a.mask_block[sched_off + s] * kBq : 0;
+          if (elect_one()) {
+            mbar_arrive_expect_tx(SPLASH_BAR(aux_full, slot), bytes);
+            if (a.has_seg)
+              bulk_load_1d(seg_u32 + slot * L::kSegStage, a.seg_kv + static_cast<size_t>(b) * a.kv_len + j * BKV,
+                           L::kSegStage, SPLASH_BAR(aux_full, slot));
+            if (partial_dense) {
 #pragma unroll
-            for (int t = 0; t < NT; ++t)
-              tma_load_2d(mask_u32 + slot * L::kMaskStage + t * (kTile * BKV), &tm_mask, 0, mrow + t * kTile,
-                          SPLASH_BAR(aux_full, slot));
+              for (int t = 0; t < NT; ++t)
+                tma_load_2d(mask_u32 + slot * L::kMaskStage + t * (kTile * BKV), &tm_mask, 0, mrow + t * kTile,
+                            SPLASH_BAR(aux_full, slot));
+            }
           }
         }
         if (++slot == stages) { slot = 0; phase ^= 1; }
       }
-    } else if (warp == kSoftmaxWarps + 1 && lane == 0 && n > 0) {
+    } else if (warp == kSoftmaxWarps + 1 && n > 0) {
       // ------------------------------- MMA issuer -------------------------------
+      // All lanes run the loop; one elected lane issues each instruction.
       // S_t = Q_t K^T: both operands K-major, 64-element (128-byte) boxes side by side.
       auto issue_qk = [&](int t, int kslot, uint32_t s_dst) {
         const uint32_t a_lo = desc_lo(q_u32 + t * (kTile * D * 2), 16);
@@ -245,7 +256,7 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t ao = ((kk / 4) * (kTile * 128) + (kk % 4) * 32) >> 4;
           const uint32_t bo = ((kk / 4) * (BKV * 128) + (kk % 4) * 32) >> 4;
-          umma_ss2(s_dst, a_lo + ao, kDescHi, b_lo + bo, kDescHi, kIdescQK, kk > 0);
+          umma_ss2_w(s_dst, a_lo + ao, kDescHi, b_lo + bo, kDescHi, kIdescQK, kk > 0);
         }
       };
       // O_t (+)= P_t V: P from tensor memory (8 columns per 16 keys), V MN-major.
@@ -253,20 +264,20 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const uint32_t b_lo = desc_lo(v_u32 + vslot * L::kVStage, BKV * 128);
 #pragma unroll
         for (int kk = 0; kk < BKV / 16; ++kk)
-          umma_ts2(tmem + 2 * BKV + t * DV, p_src + kk * 8, b_lo + ((kk * 2048) >> 4), kDescHi, kIdescPV,
+          umma_ts2_w(tmem + 2 * BKV + t * DV, p_src + kk * 8, b_lo + ((kk * 2048) >> 4), kDescHi, kIdescPV,
                    kk > 0 ? 1u : acc);
       };
-      bool ok = mbar_wait(SPLASH_BAR(q_full, 0), 0, ctx, kSiteMmaQ, 0) &&
-                mbar_wait(SPLASH_BAR(k_full, 0), 0, ctx, kSiteMmaK, 0);
+      bool ok = warp_wait(SPLASH_BAR(q_full, 0), 0, ctx, kSiteMmaQ, 0) &&
+                warp_wait(SPLASH_BAR(k_full, 0), 0, ctx, kSiteMmaK, 0);
       if (ok) {
         tc_fence_after();
         issue_qk(0, 0, tmem);
-        umma_commit(SPLASH_BAR(s_ready, 0));
+        umma_commit_w(SPLASH_BAR(s_ready, 0));
         if constexpr (NT == 2) {
           issue_qk(1, 0, tmem + BKV);
-          umma_commit(SPLASH_BAR(s_ready, 1));
+          umma_commit_w(SPLASH_BAR(s_ready, 1));
         }
-        umma_commit(SPLASH_BAR(k_empty, 0));
+        umma_commit_w(SPLASH_BAR(k_empty, 0));
         int slot = 0;
         uint32_t phase = 0;
         for (int s = 0; s < n; ++s) {
@@ -277,43 +288,43 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           if constexpr (NT == 1) {
             const int cur = s & 1;
             if (next) {
-              if (!mbar_wait(SPLASH_BAR(k_full, slot1), phase1, ctx, kSiteMmaK, s + 1)) break;
+              if (!warp_wait(SPLASH_BAR(k_full, slot1), phase1, ctx, kSiteMmaK, s + 1)) break;
               tc_fence_after();
               issue_qk(0, slot1, tmem + (cur ^ 1) * BKV);
-              umma_commit(SPLASH_BAR(s_ready, cur ^ 1));
-              umma_commit(SPLASH_BAR(k_empty, slot1));
+              umma_commit_w(SPLASH_BAR(s_ready, cur ^ 1));
+              umma_commit_w(SPLASH_BAR(k_empty, slot1));
             }
-            if (!mbar_wait(SPLASH_BAR(v_full, slot), phase, ctx, kSiteMmaV, s)) break;
-            if (!mbar_wait(SPLASH_BAR(p_ready, cur), (s >> 1) & 1, ctx, kSiteMmaP, s)) break;
+            if (!warp_wait(SPLASH_BAR(v_full, slot), phase, ctx, kSiteMmaV, s)) break;
+            if (!warp_wait(SPLASH_BAR(p_ready, cur), (s >> 1) & 1, ctx, kSiteMmaP, s)) break;
             tc_fence_after();
             issue_pv(0, slot, tmem + cur * BKV, s > 0);
-            umma_commit(SPLASH_BAR(v_empty, slot));
-            umma_commit(SPLASH_BAR(pv_done, 0));
+            umma_commit_w(SPLASH_BAR(v_empty, slot));
+            umma_commit_w(SPLASH_BAR(pv_done, 0));
           } else {
-            if (!mbar_wait(SPLASH_BAR(v_full, slot), phase, ctx, kSiteMmaV, s)) break;
-            if (!mbar_wait(SPLASH_BAR(p_ready, 0), s & 1, ctx, kSiteMmaP, s)) break;
+            if (!warp_wait(SPLASH_BAR(v_full, slot), phase, ctx, kSiteMmaV, s)) break;
+            if (!warp_wait(SPLASH_BAR(p_ready, 0), s & 1, ctx, kSiteMmaP, s)) break;
             tc_fence_after();
             issue_pv(0, slot, tmem, s > 0);
             if (next) {
-              if (!mbar_wait(SPLASH_BAR(k_full, slot1), phase1, ctx, kSiteMmaK, s + 1)) break;
+              if (!warp_wait(SPLASH_BAR(k_full, slot1), phase1, ctx, kSiteMmaK, s + 1)) break;
               tc_fence_after();
               issue_qk(0, slot1, tmem);
-              umma_commit(SPLASH_BAR(s_ready, 0));
+              umma_commit_w(SPLASH_BAR(s_ready, 0));
             }
-            if (!mbar_wait(SPLASH_BAR(p_ready, 1), s & 1, ctx, kSiteMmaP, s)) break;
+            if (!warp_wait(SPLASH_BAR(p_ready, 1), s & 1, ctx, kSiteMmaP, s)) break;
             tc_fence_after();
             issue_pv(1, slot, tmem + BKV, s > 0);
-            umma_commit(SPLASH_BAR(v_empty, slot));
+            umma_commit_w(SPLASH_BAR(v_empty, slot));
             if (next) {
               issue_qk(1, slot1, tmem + BKV);
-              umma_commit(SPLASH_BAR(s_ready, 1));
-              umma_commit(SPLASH_BAR(k_empty, slot1));
+              umma_commit_w(SPLASH_BAR(s_ready, 1));
+              umma_commit_w(SPLASH_BAR(k_empty, slot1));
             }
           }
           slot = slot1;
           phase = phase1;
         }
-        if constexpr (NT == 2) umma_commit(SPLASH_BAR(o_done, 0));
+        if constexpr (NT == 2) umma_commit_w(SPLASH_BAR(o_done, 0));
       }
     }
   } else {
