@@ -109,13 +109,10 @@ extern "C" int splash_bwd_dkv(const SplashParams* p, void* stream) {
   if (int rc = check_bwd(p)) return rc;
   if (!p->dk || !p->dv) return fail(SPLASH_INVALID_ARGUMENT, "dk / dv is null");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // Tensor memory holds S^T, dP^T, P^T, dS^T, dK and dV at once: 128 q rows per step
-  // fit at head_dim 64, 64 q rows at head_dim 128.
-  if (p->head_dim == 64) {
-    if (p->sub_block == 64) return launch_bwd_col<64, 64, 64, false>(*p, st);
-    return launch_bwd_col<64, 64, 128, false>(*p, st);
-  }
-  return launch_bwd_col<128, 128, 64, false>(*p, st);
+  // The kernel works in steps of 64 q rows with double-buffered scores; `sub_block`
+  // is accepted for compatibility and does not change the tiling.
+  if (p->head_dim == 64) return launch_bwd_col<64, false>(*p, st);
+  return launch_bwd_col<128, false>(*p, st);
 }
 
 extern "C" int64_t splash_bwd_fused_workspace_bytes(const SplashParams* p) {
@@ -129,7 +126,7 @@ extern "C" int splash_bwd_fused(const SplashParams* p, void* stream) {
   if (p->head_dim != 128) return fail(SPLASH_UNSUPPORTED, "the fused backward is compiled for head_dim 128");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   SPLASH_CUDA_CHECK(cudaMemsetAsync(p->dq_acc, 0, static_cast<size_t>(splash_bwd_fused_workspace_bytes(p)), st));
-  if (int rc = launch_bwd_col<128, 128, 64, true>(*p, st)) return rc;
+  if (int rc = launch_bwd_col<128, true>(*p, st)) return rc;
   return launch_dq_transpose_cast(p->dq_acc, p->dq, static_cast<long long>(p->batch) * p->heads, p->head_dim, p->q_len,
                                   p->dtype, st);
 }

@@ -9,16 +9,22 @@
 //                   f32 accumulator laid out [batch, heads, head_dim, q_len] with a
 //                   TMA add-reduction (head_dim 128, 64 q rows per step).
 //
-// Per step (BC q rows of one q block):
-//   S^T  = K Q^T        smem x smem -> TMEM f32   [128 kv, BC]
+// Per step (64 q rows of one q block):
+//   S^T  = K Q^T        smem x smem -> TMEM f32   [128 kv, 64]
 //   dP^T = V dO^T       smem x smem -> TMEM f32
-//   elementwise (thread = kv row, two warpgroups split the BC columns):
+//   elementwise (thread = kv row, two warpgroups split the 64 columns):
 //     P^T  = exp2((S^T - lse) log2e)   masked entries 0
 //     dS^T = P^T (dP^T - delta) [ (1 - tanh^2) with soft-cap ]
-//     both written to TMEM as packed 16-bit; FUSED also stages dS^T in shared memory
+//     both written back over the columns they came from as packed 16-bit; FUSED also
+//     stages dS^T in shared memory
 //   dV  += P^T dO       TMEM x smem
 //   dK  += dS^T Q       TMEM x smem
-//   dQ^T = K^T dS^T     smem x smem (FUSED), drained by a writer warpgroup
+//   dQ^T = K^T dS^T     smem x smem (FUSED), written over the dead S^T columns and
+//                       drained by a writer warpgroup
+//
+// S^T and dP^T are double-buffered in tensor memory: the scores of step t+2 are issued
+// while the elementwise warps work on step t+1, so the tensor core and the elementwise
+// warps overlap instead of taking turns.  That needs three Q/dO tiles in flight.
 //
 // Behaviour follows the reference kernels (splash_attention_mgpu/backward.py:377-785,
 // backward_fused.py:64-512); the code shares nothing with them.
@@ -55,27 +61,30 @@ struct BwdArgs {
 
 enum BwdSite : int {
   kBSiteTmaEmpty = 21, kBSiteMmaKV, kBSiteMmaFull, kBSiteMmaP, kBSiteMmaDqFree,
-  kBSiteEwFull, kBSiteEwS, kBSiteEwPds, kBSiteEwDone, kBSiteEwEpi,
+  kBSiteEwFull, kBSiteEwS, kBSiteEwDone, kBSiteEwEpi,
   kBSiteWrReady, kBSiteWrBarA, kBSiteWrBarB,
 };
 
-template <int D, int DV, int BC, bool FUSED>
+constexpr int kColBC = 64;  // q rows per step
+
+template <int D, bool FUSED>
 struct ColLayout {
   static constexpr int kRows = 128;  // kv rows per CTA
+  static constexpr int BC = kColBC;
   static constexpr int kSub = 128 / BC;
   static constexpr int kKBytes = kRows * D * 2;
-  static constexpr int kVBytes = kRows * DV * 2;
+  static constexpr int kVBytes = kRows * D * 2;
   static constexpr int kQStage = BC * D * 2;
-  static constexpr int kDoStage = BC * DV * 2;
+  static constexpr int kDoStage = BC * D * 2;
   static constexpr int kVecStage = BC * 4;          // lse, delta, q segment ids: BC words each
   static constexpr int kMaskStage = kRows * BC;     // int8, transposed block slice
   static constexpr int kDsStage = kRows * BC * 2;   // FUSED: dS^T as an MMA operand
-  static constexpr int kDqStage = 128 * BC * 4;     // FUSED: dQ^T tile, f32
-  // Tensor memory columns.
-  static constexpr int kColS = 0, kColDp = BC, kColP = 2 * BC, kColDs = 2 * BC + BC / 2;
-  static constexpr int kColDk = 3 * BC, kColDv = 3 * BC + D, kColDq = 3 * BC + D + DV;
-  static constexpr int kTmemUsed = 3 * BC + D + DV + (FUSED ? BC : 0);
-  static constexpr int kTmemCols = kTmemUsed <= 256 ? 256 : 512;
+  static constexpr int kDqStage = 128 * 32 * 4;     // FUSED: half a dQ^T tile (32 q columns), f32
+  // Tensor memory columns: two S^T buffers, two dP^T buffers, dK, dV.  P^T lives in the
+  // S^T buffer it came from, dS^T in the dP^T buffer, dQ^T reuses the S^T buffer.
+  static constexpr int kColS = 0, kColDp = 2 * BC, kColDk = 4 * BC, kColDv = 4 * BC + D;
+  static constexpr int kTmemUsed = 4 * BC + 2 * D;
+  static constexpr int kTmemCols = 512;
   static constexpr int kEwThreads = 256;
   static constexpr int kThreads = kEwThreads + (FUSED ? 128 : 0) + 128;
   static_assert(kTmemUsed <= 512, "tensor memory budget");
@@ -97,7 +106,7 @@ constexpr int kBwdMaxStages = 4;
 struct ColBarriers {
   uint64_t kv_full;
   uint64_t full[kBwdMaxStages], empty[kBwdMaxStages];
-  uint64_t s_ready, p_ready, pds_free, acc_done;
+  uint64_t s_ready[2], p_ready[2], acc_done;
   uint64_t dq_ready, dq_free, wr_a, wr_b;
   uint64_t epi[2];
   uint32_t tmem_base;
@@ -150,20 +159,20 @@ struct ColSteps {
   }
 };
 
-template <int D, int DV, int BC, bool FUSED, bool BF16>
-__global__ void __launch_bounds__(ColLayout<D, DV, BC, FUSED>::kThreads, 1)
+template <int D, bool FUSED, bool BF16>
+__global__ void __launch_bounds__(ColLayout<D, FUSED>::kThreads, 1)
 splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
                       const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv,
                       const __grid_constant__ CUtensorMap tm_mask, const __grid_constant__ CUtensorMap tm_dqacc,
                       const BwdArgs a) {
-  using L = ColLayout<D, DV, BC, FUSED>;
+  using L = ColLayout<D, FUSED>;
   constexpr int kRows = 128;
+  constexpr int BC = kColBC;
   constexpr int kSub = L::kSub;
   constexpr int kEwWarps = 8;
   constexpr int kWriterWarp0 = kEwWarps;                       // FUSED only
   constexpr int kProducerWarp0 = kEwWarps + (FUSED ? 4 : 0);
-  constexpr int kHalf = BC / 2;                                // columns per elementwise warpgroup
 
   extern __shared__ uint8_t smem_raw[];
   const int stages = a.stages;
@@ -182,7 +191,7 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const uint32_t dead_u32 = bars_u32 + static_cast<uint32_t>(offsetof(ColBarriers, dead));
   const uint32_t tmem_slot_u32 = bars_u32 + static_cast<uint32_t>(offsetof(ColBarriers, tmem_base));
 
-  const int warp = threadIdx.x >> 5;
+  const int warp = uniform_warp_index();
   const int lane = threadIdx.x & 31;
 
   // ---- which KV block ----------------------------------------------------------
@@ -209,16 +218,16 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       mbar_init(SPLASH_CBAR(full, i), 1);
       mbar_init(SPLASH_CBAR(empty, i), 1 + kEwWarps);
     }
-    mbar_init(SPLASH_CBAR(s_ready, 0), 1);
-    mbar_init(SPLASH_CBAR(p_ready, 0), L::kEwThreads);
-    mbar_init(SPLASH_CBAR(pds_free, 0), 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(SPLASH_CBAR(s_ready, i), 1);
+      mbar_init(SPLASH_CBAR(p_ready, i), L::kEwThreads);
+      mbar_init(SPLASH_CBAR(epi, i), 128);
+    }
     mbar_init(SPLASH_CBAR(acc_done, 0), 1);
     mbar_init(SPLASH_CBAR(dq_ready, 0), 1);
     mbar_init(SPLASH_CBAR(dq_free, 0), 128);
     mbar_init(SPLASH_CBAR(wr_a, 0), 128);
     mbar_init(SPLASH_CBAR(wr_b, 0), 128);
-    mbar_init(SPLASH_CBAR(epi, 0), 128);
-    mbar_init(SPLASH_CBAR(epi, 1), 128);
     fence_mbar_init();
     fence_proxy_async_smem();
   }
@@ -236,121 +245,134 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   constexpr uint32_t kDescHi = desc_hi(1024);
 
   if (warp >= kProducerWarp0) {
-    if (warp == kProducerWarp0 && lane == 0 && total > 0) {
+    if (warp == kProducerWarp0 && total > 0) {
       // ------------------------------ TMA producer ------------------------------
-      prefetch_tensormap(&tm_q);
-      prefetch_tensormap(&tm_do);
-      mbar_arrive_expect_tx(SPLASH_CBAR(kv_full, 0), L::kKBytes + L::kVBytes);
+      // Warp-uniform loop; one elected lane issues each group of copies.
+      if (elect_one()) {
+        prefetch_tensormap(&tm_q);
+        prefetch_tensormap(&tm_do);
+        mbar_arrive_expect_tx(SPLASH_CBAR(kv_full, 0), L::kKBytes + L::kVBytes);
 #pragma unroll
-      for (int c = 0; c < D / 64; ++c)
-        tma_load_2d(k_u32 + c * (kRows * 128), &tm_k, c * 64, kv_row0, SPLASH_CBAR(kv_full, 0));
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_2d(k_u32 + c * (kRows * 128), &tm_k, c * 64, kv_row0, SPLASH_CBAR(kv_full, 0));
 #pragma unroll
-      for (int c = 0; c < DV / 64; ++c)
-        tma_load_2d(v_u32 + c * (kRows * 128), &tm_v, c * 64, kv_row0, SPLASH_CBAR(kv_full, 0));
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_2d(v_u32 + c * (kRows * 128), &tm_v, c * 64, kv_row0, SPLASH_CBAR(kv_full, 0));
+      }
       int slot = 0;
       uint32_t phase = 0;
       for (int t = 0; it.valid(); it.next(), ++t) {
         const int off = it.off();
         const int qblk = a.block_list[off];
         const int q_row = (b * a.heads + it.head()) * a.q_len + qblk * 128 + it.sb * BC;
-        if (t >= stages && !mbar_wait(SPLASH_CBAR(empty, slot), phase ^ 1, ctx, kBSiteTmaEmpty, t)) break;
+        if (t >= stages && !warp_wait(SPLASH_CBAR(empty, slot), phase ^ 1, ctx, kBSiteTmaEmpty, t)) break;
         const bool partial_dense = a.has_dense && a.block_kind[off] == SPLASH_BLOCK_PARTIAL;
         const uint32_t bytes = L::kQStage + L::kDoStage + 2 * L::kVecStage + (a.has_seg ? L::kVecStage : 0) +
                                (partial_dense ? L::kMaskStage : 0);
         const uint32_t bar = SPLASH_CBAR(full, slot);
-        mbar_arrive_expect_tx(bar, bytes);
+        const int mrow = partial_dense ? a.mask_block[off] * 128 : 0;
+        if (elect_one()) {
+          mbar_arrive_expect_tx(bar, bytes);
 #pragma unroll
-        for (int c = 0; c < D / 64; ++c)
-          tma_load_2d(q_u32 + slot * L::kQStage + c * (BC * 128), &tm_q, c * 64, q_row, bar);
+          for (int c = 0; c < D / 64; ++c)
+            tma_load_2d(q_u32 + slot * L::kQStage + c * (BC * 128), &tm_q, c * 64, q_row, bar);
 #pragma unroll
-        for (int c = 0; c < DV / 64; ++c)
-          tma_load_2d(do_u32 + slot * L::kDoStage + c * (BC * 128), &tm_do, c * 64, q_row, bar);
-        bulk_load_1d(lse_u32 + slot * L::kVecStage, a.lse + q_row, L::kVecStage, bar);
-        bulk_load_1d(delta_u32 + slot * L::kVecStage, a.delta + q_row, L::kVecStage, bar);
-        if (a.has_seg)
-          bulk_load_1d(segq_u32 + slot * L::kVecStage,
-                       a.seg_q + static_cast<size_t>(b) * a.q_len + qblk * 128 + it.sb * BC, L::kVecStage, bar);
-        if (partial_dense)
-          tma_load_2d(mask_u32 + slot * L::kMaskStage, &tm_mask, it.sb * BC, a.mask_block[off] * 128, bar);
+          for (int c = 0; c < D / 64; ++c)
+            tma_load_2d(do_u32 + slot * L::kDoStage + c * (BC * 128), &tm_do, c * 64, q_row, bar);
+          bulk_load_1d(lse_u32 + slot * L::kVecStage, a.lse + q_row, L::kVecStage, bar);
+          bulk_load_1d(delta_u32 + slot * L::kVecStage, a.delta + q_row, L::kVecStage, bar);
+          if (a.has_seg)
+            bulk_load_1d(segq_u32 + slot * L::kVecStage,
+                         a.seg_q + static_cast<size_t>(b) * a.q_len + qblk * 128 + it.sb * BC, L::kVecStage, bar);
+          if (partial_dense) tma_load_2d(mask_u32 + slot * L::kMaskStage, &tm_mask, it.sb * BC, mrow, bar);
+        }
         if (++slot == stages) { slot = 0; phase ^= 1; }
       }
-    } else if (warp == kProducerWarp0 + 1 && lane == 0 && total > 0) {
+    } else if (warp == kProducerWarp0 + 1 && total > 0) {
       // ------------------------------- MMA issuer -------------------------------
+      // All lanes run the loop; one elected lane issues each instruction.
       constexpr uint32_t kIdescScore = make_idesc(BF16, 128, BC, false, false);   // K Q^T, V dO^T
-      constexpr uint32_t kIdescDv = make_idesc(BF16, 128, DV, false, true);       // P^T dO
-      constexpr uint32_t kIdescDk = make_idesc(BF16, 128, D, false, true);        // dS^T Q
+      constexpr uint32_t kIdescAcc = make_idesc(BF16, 128, D, false, true);       // P^T dO, dS^T Q
       constexpr uint32_t kIdescDq = make_idesc(BF16, 128, BC, true, true);        // K^T dS^T
-      auto issue_scores = [&](int slot) {
+      auto issue_s = [&](int slot, int buf) {
         const uint32_t k_lo = desc_lo(k_u32, 16), q_lo = desc_lo(q_u32 + slot * L::kQStage, 16);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          umma_ss2(tmem + L::kColS, k_lo + (((kk / 4) * (kRows * 128) + (kk % 4) * 32) >> 4), kDescHi,
-                   q_lo + (((kk / 4) * (BC * 128) + (kk % 4) * 32) >> 4), kDescHi, kIdescScore, kk > 0);
+          umma_ss2_w(tmem + L::kColS + buf * BC, k_lo + (((kk / 4) * (kRows * 128) + (kk % 4) * 32) >> 4), kDescHi,
+                     q_lo + (((kk / 4) * (BC * 128) + (kk % 4) * 32) >> 4), kDescHi, kIdescScore, kk > 0);
+      };
+      auto issue_dp = [&](int slot, int buf) {
         const uint32_t v_lo = desc_lo(v_u32, 16), do_lo = desc_lo(do_u32 + slot * L::kDoStage, 16);
 #pragma unroll
-        for (int kk = 0; kk < DV / 16; ++kk)
-          umma_ss2(tmem + L::kColDp, v_lo + (((kk / 4) * (kRows * 128) + (kk % 4) * 32) >> 4), kDescHi,
-                   do_lo + (((kk / 4) * (BC * 128) + (kk % 4) * 32) >> 4), kDescHi, kIdescScore, kk > 0);
+        for (int kk = 0; kk < D / 16; ++kk)
+          umma_ss2_w(tmem + L::kColDp + buf * BC, v_lo + (((kk / 4) * (kRows * 128) + (kk % 4) * 32) >> 4), kDescHi,
+                     do_lo + (((kk / 4) * (BC * 128) + (kk % 4) * 32) >> 4), kDescHi, kIdescScore, kk > 0);
       };
-      bool ok = mbar_wait(SPLASH_CBAR(kv_full, 0), 0, ctx, kBSiteMmaKV, 0) &&
-                mbar_wait(SPLASH_CBAR(full, 0), 0, ctx, kBSiteMmaFull, 0);
-      if (ok) {
+      int s_slot = 0;        // ring position of the next step whose scores get issued
+      uint32_t s_phase = 0;
+      bool ok = warp_wait(SPLASH_CBAR(kv_full, 0), 0, ctx, kBSiteMmaKV, 0);
+      // Prologue: scores of steps 0 and 1 fill the two buffers.
+      for (int u = 0; u < 2 && u < total && ok; ++u) {
+        ok = warp_wait(SPLASH_CBAR(full, s_slot), s_phase, ctx, kBSiteMmaFull, u);
+        if (!ok) break;
         tc_fence_after();
-        issue_scores(0);
-        umma_commit(SPLASH_CBAR(s_ready, 0));
-        int slot = 0;
-        uint32_t phase = 0;
+        issue_dp(s_slot, u);
+        issue_s(s_slot, u);
+        umma_commit_w(SPLASH_CBAR(s_ready, u));
+        if (++s_slot == stages) { s_slot = 0; s_phase ^= 1; }
+      }
+      if (ok) {
+        int c_slot = 0;  // ring position of the step whose P^T / dS^T get consumed
         for (int t = 0; t < total; ++t) {
-          int slot1 = slot + 1;
-          uint32_t phase1 = phase;
-          if (slot1 == stages) { slot1 = 0; phase1 ^= 1; }
-          if (!mbar_wait(SPLASH_CBAR(p_ready, 0), t & 1, ctx, kBSiteMmaP, t)) break;
+          const int buf = t & 1;
+          if (!warp_wait(SPLASH_CBAR(p_ready, buf), (t >> 1) & 1, ctx, kBSiteMmaP, t)) break;
           tc_fence_after();
-          auto issue_next_scores = [&]() -> bool {
-            if (t + 1 >= total) return true;
-            if (!mbar_wait(SPLASH_CBAR(full, slot1), phase1, ctx, kBSiteMmaFull, t + 1)) return false;
-            tc_fence_after();
-            issue_scores(slot1);
-            umma_commit(SPLASH_CBAR(s_ready, 0));
-            return true;
-          };
-          // S^T / dP^T of step t have been read, so the next scores go first: the
-          // elementwise warps start on them while dV, dK (and dQ) of step t still run.
-          // (With a single stage the next Q/dO tile only arrives after dK has released
-          // this one, so the order is the other way round.)
-          if (stages > 1 && !issue_next_scores()) break;
           {
-            // dV += P^T dO ; dK += dS^T Q   (B operands MN-major: boxes of 64 columns, BC rows each)
-            const uint32_t do_lo = desc_lo(do_u32 + slot * L::kDoStage, BC * 128);
-            const uint32_t q_lo = desc_lo(q_u32 + slot * L::kQStage, BC * 128);
+            // dV += P^T dO ; dK += dS^T Q.  A operands are the packed 16-bit values the
+            // elementwise warps wrote over S^T / dP^T: keys 0-31 sit in columns 0-15 of the
+            // buffer, keys 32-63 in columns 32-47 (each warpgroup packs into its own half).
+            // B operands MN-major: boxes of 64 columns, BC rows each.
+            const uint32_t do_lo = desc_lo(do_u32 + c_slot * L::kDoStage, BC * 128);
+            const uint32_t q_lo = desc_lo(q_u32 + c_slot * L::kQStage, BC * 128);
 #pragma unroll
             for (int kk = 0; kk < BC / 16; ++kk)
-              umma_ts2(tmem + L::kColDv, tmem + L::kColP + kk * 8, do_lo + ((kk * 2048) >> 4), kDescHi, kIdescDv,
-                       (t > 0 || kk > 0) ? 1u : 0u);
+              umma_ts2_w(tmem + L::kColDv, tmem + L::kColS + buf * BC + (kk >> 1) * 32 + (kk & 1) * 8,
+                         do_lo + ((kk * 2048) >> 4), kDescHi, kIdescAcc, (t > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
             for (int kk = 0; kk < BC / 16; ++kk)
-              umma_ts2(tmem + L::kColDk, tmem + L::kColDs + kk * 8, q_lo + ((kk * 2048) >> 4), kDescHi, kIdescDk,
-                       (t > 0 || kk > 0) ? 1u : 0u);
+              umma_ts2_w(tmem + L::kColDk, tmem + L::kColDp + buf * BC + (kk >> 1) * 32 + (kk & 1) * 8,
+                         q_lo + ((kk * 2048) >> 4), kDescHi, kIdescAcc, (t > 0 || kk > 0) ? 1u : 0u);
           }
-          umma_commit(SPLASH_CBAR(empty, slot));
-          umma_commit(SPLASH_CBAR(pds_free, 0));  // P^T / dS^T of step t may be overwritten
-          if (stages == 1 && !issue_next_scores()) break;
+          umma_commit_w(SPLASH_CBAR(empty, c_slot));
           if constexpr (FUSED) {
-            if (t > 0 && !mbar_wait(SPLASH_CBAR(dq_free, 0), (t - 1) & 1, ctx, kBSiteMmaDqFree, t)) break;
-            tc_fence_after();
-            // dQ^T[d, q] = sum_kv K[kv, d] dS^T[kv, q]: A = K read MN-major, B = staged dS^T MN-major.
+            // dQ^T[d, q] = sum_kv K[kv, d] dS^T[kv, q]: A = K read MN-major, B = staged dS^T
+            // MN-major.  The result replaces S^T / P^T of this step, which dV has consumed
+            // (the tensor core runs its instructions in issue order).
             const uint32_t k_lo = desc_lo(k_u32, kRows * 128);
-            const uint32_t ds_lo = desc_lo(ds_u32 + (t & 1) * L::kDsStage, kRows * 128);
+            const uint32_t ds_lo = desc_lo(ds_u32 + buf * L::kDsStage, kRows * 128);
 #pragma unroll
             for (int kk = 0; kk < kRows / 16; ++kk)
-              umma_ss2(tmem + L::kColDq, k_lo + ((kk * 2048) >> 4), kDescHi, ds_lo + ((kk * 2048) >> 4), kDescHi,
-                       kIdescDq, kk > 0);
-            umma_commit(SPLASH_CBAR(dq_ready, 0));
+              umma_ss2_w(tmem + L::kColS + buf * BC, k_lo + ((kk * 2048) >> 4), kDescHi, ds_lo + ((kk * 2048) >> 4),
+                         kDescHi, kIdescDq, kk > 0);
+            umma_commit_w(SPLASH_CBAR(dq_ready, 0));
           }
-          slot = slot1;
-          phase = phase1;
+          if (t + 2 < total) {
+            // Scores of step t+2 go into the buffers step t has just vacated.
+            if (!warp_wait(SPLASH_CBAR(full, s_slot), s_phase, ctx, kBSiteMmaFull, t + 2)) break;
+            tc_fence_after();
+            issue_dp(s_slot, buf);
+            if constexpr (FUSED) {
+              // The writer must have taken dQ^T of step t out of the S^T buffer.
+              if (!warp_wait(SPLASH_CBAR(dq_free, 0), t & 1, ctx, kBSiteMmaDqFree, t)) break;
+              tc_fence_after();
+            }
+            issue_s(s_slot, buf);
+            umma_commit_w(SPLASH_CBAR(s_ready, buf));
+            if (++s_slot == stages) { s_slot = 0; s_phase ^= 1; }
+          }
+          if (++c_slot == stages) c_slot = 0;
         }
-        umma_commit(SPLASH_CBAR(acc_done, 0));
+        umma_commit_w(SPLASH_CBAR(acc_done, 0));
       }
     }
   } else if (FUSED && warp >= kWriterWarp0) {
@@ -358,50 +380,53 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     if constexpr (FUSED) {
       const int wq = warp & 3;
       const int drow = wq * 32 + lane;  // head-dim index = TMEM lane
-      const uint32_t dq_tmem = tmem + (static_cast<uint32_t>(wq * 32) << 16) + L::kColDq;
+      const uint32_t dq_tmem = tmem + (static_cast<uint32_t>(wq * 32) << 16) + L::kColS;
       const bool leader = (warp == kWriterWarp0 && lane == 0);
+      bool alive = true;
       int t = 0;
-      for (; it.valid(); it.next(), ++t) {
+      for (; it.valid() && alive; it.next(), ++t) {
         const int qblk = a.block_list[it.off()];
         if (!warp_wait(SPLASH_CBAR(dq_ready, 0), t & 1, ctx, kBSiteWrReady, t)) break;
         tc_fence_after();
         uint32_t acc[BC];
 #pragma unroll
-        for (int c = 0; c < BC / 32; ++c) tmem_ld32(dq_tmem + c * 32, acc + c * 32);
+        for (int c = 0; c < BC / 32; ++c) tmem_ld32(dq_tmem + (t & 1) * BC + c * 32, acc + c * 32);
         tmem_wait_ld();
         tc_fence_before();
         mbar_arrive(SPLASH_CBAR(dq_free, 0));
-        // The previous tile's reduction must have read the staging buffer.
-        if (leader) bulk_wait_group_read<0>();
-        mbar_arrive(SPLASH_CBAR(wr_a, 0));
-        if (!warp_wait(SPLASH_CBAR(wr_a, 0), t & 1, ctx, kBSiteWrBarA, t)) break;
+        const int x = qblk * 128 + it.sb * BC;
+        const int y = (b * a.heads + it.head()) * D;
+        // Two passes of 32 q columns through one 16 KB staging tile (128 rows of 128 bytes).
 #pragma unroll
-        for (int c = 0; c < BC / 4; ++c) {
-          // 32 f32 (128 bytes) per row and box; boxes of 32 q columns side by side.
-          const uint32_t box = dqs_u32 + (c / 8) * (128 * 128);
-          sts128(box + swz128(drow, c & 7), make_uint4(acc[c * 4], acc[c * 4 + 1], acc[c * 4 + 2], acc[c * 4 + 3]));
-        }
-        fence_proxy_async_smem();
-        mbar_arrive(SPLASH_CBAR(wr_b, 0));
-        if (!warp_wait(SPLASH_CBAR(wr_b, 0), t & 1, ctx, kBSiteWrBarB, t)) break;
-        if (leader) {
-          const int x = qblk * 128 + it.sb * BC;
-          const int y = (b * a.heads + it.head()) * D;
+        for (int half = 0; half < 2; ++half) {
+          const uint32_t par = (2 * t + half) & 1;
+          // The previous reduction must have read the staging tile.
+          if (leader) bulk_wait_group_read<0>();
+          mbar_arrive(SPLASH_CBAR(wr_a, 0));
+          if (!warp_wait(SPLASH_CBAR(wr_a, 0), par, ctx, kBSiteWrBarA, t)) { alive = false; break; }
 #pragma unroll
-          for (int c = 0; c < BC / 32; ++c) tma_reduce_add_2d(&tm_dqacc, dqs_u32 + c * (128 * 128), x + c * 32, y);
-          bulk_commit_group();
+          for (int c = 0; c < 8; ++c)
+            sts128(dqs_u32 + swz128(drow, c), make_uint4(acc[half * 32 + c * 4], acc[half * 32 + c * 4 + 1],
+                                                         acc[half * 32 + c * 4 + 2], acc[half * 32 + c * 4 + 3]));
+          fence_proxy_async_smem();
+          mbar_arrive(SPLASH_CBAR(wr_b, 0));
+          if (!warp_wait(SPLASH_CBAR(wr_b, 0), par, ctx, kBSiteWrBarB, t)) { alive = false; break; }
+          if (leader) {
+            tma_reduce_add_2d(&tm_dqacc, dqs_u32, x + half * 32, y);
+            bulk_commit_group();
+          }
         }
       }
       if (leader) bulk_wait_group<0>();
     }
   } else {
     // ========================== elementwise warpgroups ===========================
-    const int w = warp >> 2;                 // which half of the BC columns
+    const int w = warp >> 2;                 // which half of the 64 columns
     const int wq = warp & 3;
     const int row = wq * 32 + lane;          // kv row inside the block
     const int kv_pos = kj * kRows + row;
     const uint32_t tmem_row = tmem + (static_cast<uint32_t>(wq * 32) << 16);
-    const int col0 = w * kHalf;              // first column this thread handles
+    const int col0 = w * 32;                 // first column this thread handles
 
     if (total == 0) {
       // No q block sees this KV block: its gradients are zero.
@@ -410,9 +435,9 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 #pragma unroll
         for (int c = 0; c < D * 2 / 16; ++c) dst[c] = make_uint4(0, 0, 0, 0);
       } else {
-        uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(a.dv) + static_cast<size_t>(kv_row0 + row) * (DV * 2));
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(a.dv) + static_cast<size_t>(kv_row0 + row) * (D * 2));
 #pragma unroll
-        for (int c = 0; c < DV * 2 / 16; ++c) dst[c] = make_uint4(0, 0, 0, 0);
+        for (int c = 0; c < D * 2 / 16; ++c) dst[c] = make_uint4(0, 0, 0, 0);
       }
     } else {
       const int my_seg = a.has_seg ? a.seg_kv[static_cast<size_t>(b) * a.kv_len + kv_pos] : 0;
@@ -441,14 +466,15 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           }
         }
         if (!warp_wait(SPLASH_CBAR(full, slot), phase, ctx, kBSiteEwFull, t)) { alive = false; break; }
-        if (!warp_wait(SPLASH_CBAR(s_ready, 0), t & 1, ctx, kBSiteEwS, t)) { alive = false; break; }
+        const int buf = t & 1;
+        if (!warp_wait(SPLASH_CBAR(s_ready, buf), (t >> 1) & 1, ctx, kBSiteEwS, t)) { alive = false; break; }
         tc_fence_after();
         const int q0 = qblk * 128 + it.sb * BC + col0;  // sequence position of this thread's first column
-#pragma unroll
-        for (int c = 0; c < kHalf / 32; ++c) {
+        {
+          constexpr int c = 0;  // one 32-column chunk per thread and step
           uint32_t sraw[32], dpraw[32];
-          tmem_ld32(tmem_row + L::kColS + col0 + c * 32, sraw);
-          tmem_ld32(tmem_row + L::kColDp + col0 + c * 32, dpraw);
+          tmem_ld32(tmem_row + L::kColS + buf * BC + col0, sraw);
+          tmem_ld32(tmem_row + L::kColDp + buf * BC + col0, dpraw);
           tmem_wait_ld();
           uint32_t ppk[16], dspk[16];
           const uint32_t vec_off = slot * L::kVecStage + (col0 + c * 32) * 4;
@@ -535,13 +561,12 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
               dspk[g * 2 + 1] = pack2<BF16>(dsv[2], dsv[3]);
             }
           }
-          // dV / dK of the previous step must have consumed P^T / dS^T before they are replaced.
-          if (c == 0 && t > 0 && !warp_wait(SPLASH_CBAR(pds_free, 0), (t - 1) & 1, ctx, kBSiteEwPds, t)) { alive = false; break; }
-          tmem_st16(tmem_row + L::kColP + (col0 + c * 32) / 2, ppk);
-          tmem_st16(tmem_row + L::kColDs + (col0 + c * 32) / 2, dspk);
+          // Packed results go over the first half of the columns this thread just read.
+          tmem_st16(tmem_row + L::kColS + buf * BC + col0, ppk);
+          tmem_st16(tmem_row + L::kColDp + buf * BC + col0, dspk);
           if constexpr (FUSED) {
             // dS^T staged as [kv row][64 q], 128 bytes per row, 128-byte swizzle.
-            const uint32_t stage = ds_u32 + (t & 1) * L::kDsStage;
+            const uint32_t stage = ds_u32 + buf * L::kDsStage;
             const int chunk0 = (col0 + c * 32) / 8;  // 16-byte chunk index of this thread's first column
 #pragma unroll
             for (int g = 0; g < 4; ++g)
@@ -549,14 +574,13 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                      make_uint4(dspk[g * 4], dspk[g * 4 + 1], dspk[g * 4 + 2], dspk[g * 4 + 3]));
           }
         }
-        if (!alive) break;
         // The slot's vectors and mask slice have been read.
         __syncwarp();
         if (lane == 0) mbar_arrive(SPLASH_CBAR(empty, slot));
         tmem_wait_st();
         if constexpr (FUSED) fence_proxy_async_smem();
         tc_fence_before();
-        mbar_arrive(SPLASH_CBAR(p_ready, 0));
+        mbar_arrive(SPLASH_CBAR(p_ready, buf));
         if (++slot == stages) { slot = 0; phase ^= 1; }
       }
 
@@ -566,7 +590,7 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         tc_fence_after();
         const uint32_t stage = w == 0 ? k_u32 : v_u32;  // K / V tiles are dead once every MMA has finished
         const uint32_t acc_tmem = tmem_row + (w == 0 ? L::kColDk : L::kColDv);
-        constexpr int kCols = D;  // D == DV for every compiled configuration
+        constexpr int kCols = D;
 #pragma unroll
         for (int c = 0; c < kCols / 32; ++c) {
           uint32_t o[32];

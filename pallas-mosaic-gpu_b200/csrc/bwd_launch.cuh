@@ -38,15 +38,20 @@ inline void fill_bwd_args(BwdArgs& a, const SplashParams& p, bool dense, bool se
   a.soft_cap = p.soft_cap;
 }
 
-template <int D, int DV, int BC, bool FUSED, bool BF16>
+template <int D, bool FUSED, bool BF16>
 int launch_bwd_col_typed(const SplashParams& p, cudaStream_t stream) {
-  using L = ColLayout<D, DV, BC, FUSED>;
+  using L = ColLayout<D, FUSED>;
+  constexpr int BC = kColBC;
   const bool dense = p.partial_blocks != nullptr;
   const bool seg = p.seg_q != nullptr;
-  const size_t smem = L::smem_bytes(p.num_stages, dense, seg);
+  // Ring depth: the kernel keeps the Q/dO tiles of three consecutive steps in flight, so
+  // three stages (or the caller's larger request) are used when they fit, two otherwise.
+  int stages = p.num_stages < 3 ? 3 : (p.num_stages > kBwdMaxStages ? kBwdMaxStages : p.num_stages);
+  while (stages > 2 && L::smem_bytes(stages, dense, seg) > kMaxDynamicSmem) --stages;
+  const size_t smem = L::smem_bytes(stages, dense, seg);
   if (smem > kMaxDynamicSmem) {
     char d[96];
-    snprintf(d, sizeof d, "%zu > %zu bytes; reduce num_stages or the sub-block sizes", smem, kMaxDynamicSmem);
+    snprintf(d, sizeof d, "%zu > %zu bytes", smem, kMaxDynamicSmem);
     return fail(SPLASH_BUDGET_EXCEEDED, "shared memory budget exceeded", d);
   }
   const CUtensorMapDataType dt = tmap_dtype(p.dtype);
@@ -57,15 +62,15 @@ int launch_bwd_col_typed(const SplashParams& p, cudaStream_t stream) {
   memset(&tm_dqacc, 0, sizeof tm_dqacc);
   int rc;
   if ((rc = make_tmap_2d(&tm_q, p.q, dt, 2, q_rows, D, BC, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
-  if ((rc = make_tmap_2d(&tm_do, p.d_out, dt, 2, q_rows, DV, BC, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  if ((rc = make_tmap_2d(&tm_do, p.d_out, dt, 2, q_rows, D, BC, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if ((rc = make_tmap_2d(&tm_k, p.k, dt, 2, kv_rows, D, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
-  if ((rc = make_tmap_2d(&tm_v, p.v, dt, 2, kv_rows, DV, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  if ((rc = make_tmap_2d(&tm_v, p.v, dt, 2, kv_rows, D, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if ((rc = make_tmap_2d(&tm_dk, p.dk, dt, 2, kv_rows, D, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
-  if ((rc = make_tmap_2d(&tm_dv, p.dv, dt, 2, kv_rows, DV, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  if ((rc = make_tmap_2d(&tm_dv, p.dv, dt, 2, kv_rows, D, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if (dense) {
     const uint64_t mrows = static_cast<uint64_t>(p.num_partial_blocks) * 128;
     if ((rc = make_tmap_2d(&tm_mask, p.partial_blocks, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, mrows, 128, 128, BC,
-                           BC == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B)))
+                           CU_TENSOR_MAP_SWIZZLE_64B)))
       return rc;
   }
   if (FUSED) {
@@ -77,7 +82,8 @@ int launch_bwd_col_typed(const SplashParams& p, cudaStream_t stream) {
   }
   BwdArgs a;
   fill_bwd_args(a, p, dense, seg);
-  auto kernel = splash_bwd_col_kernel<D, DV, BC, FUSED, BF16>;
+  a.stages = stages;
+  auto kernel = splash_bwd_col_kernel<D, FUSED, BF16>;
   if ((rc = opt_in_smem(kernel, smem))) return rc;
   const unsigned grid = static_cast<unsigned>(a.kv_blocks) * p.kv_heads * p.batch;
   kernel<<<grid, L::kThreads, smem, stream>>>(tm_q, tm_k, tm_v, tm_do, tm_dk, tm_dv, tm_mask, tm_dqacc, a);
@@ -85,10 +91,10 @@ int launch_bwd_col_typed(const SplashParams& p, cudaStream_t stream) {
   return SPLASH_OK;
 }
 
-template <int D, int DV, int BC, bool FUSED>
+template <int D, bool FUSED>
 int launch_bwd_col(const SplashParams& p, cudaStream_t stream) {
-  if (p.dtype == SPLASH_DTYPE_BF16) return launch_bwd_col_typed<D, DV, BC, FUSED, true>(p, stream);
-  return launch_bwd_col_typed<D, DV, BC, FUSED, false>(p, stream);
+  if (p.dtype == SPLASH_DTYPE_BF16) return launch_bwd_col_typed<D, FUSED, true>(p, stream);
+  return launch_bwd_col_typed<D, FUSED, false>(p, stream);
 }
 
 template <int D, int DV, int BC>

@@ -93,7 +93,7 @@ splash_bwd_row_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const uint32_t dead_u32 = bars_u32 + static_cast<uint32_t>(offsetof(RowBarriers, dead));
   const uint32_t tmem_slot_u32 = bars_u32 + static_cast<uint32_t>(offsetof(RowBarriers, tmem_base));
 
-  const int warp = threadIdx.x >> 5;
+  const int warp = uniform_warp_index();
   const int lane = threadIdx.x & 31;
 
   const int hb_count = a.heads * a.batch;
@@ -137,44 +137,49 @@ splash_bwd_row_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   constexpr uint32_t kDescHi = desc_hi(1024);
 
   if (warp >= kEwWarps) {
-    if (warp == kEwWarps && lane == 0 && total > 0) {
+    if (warp == kEwWarps && total > 0) {
       // ------------------------------ TMA producer ------------------------------
+      // Warp-uniform loop; one elected lane issues each group of copies.
       const int kv_row0 = (b * a.kv_heads + h / (a.heads / a.kv_heads)) * a.kv_len;
-      prefetch_tensormap(&tm_k);
-      prefetch_tensormap(&tm_v);
-      mbar_arrive_expect_tx(SPLASH_RBAR(q_full, 0), L::kQBytes + L::kDoBytes);
+      if (elect_one()) {
+        prefetch_tensormap(&tm_k);
+        prefetch_tensormap(&tm_v);
+        mbar_arrive_expect_tx(SPLASH_RBAR(q_full, 0), L::kQBytes + L::kDoBytes);
 #pragma unroll
-      for (int c = 0; c < D / 64; ++c)
-        tma_load_2d(q_u32 + c * (kRows * 128), &tm_q, c * 64, q_row0, SPLASH_RBAR(q_full, 0));
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_2d(q_u32 + c * (kRows * 128), &tm_q, c * 64, q_row0, SPLASH_RBAR(q_full, 0));
 #pragma unroll
-      for (int c = 0; c < DV / 64; ++c)
-        tma_load_2d(do_u32 + c * (kRows * 128), &tm_do, c * 64, q_row0, SPLASH_RBAR(q_full, 0));
+        for (int c = 0; c < DV / 64; ++c)
+          tma_load_2d(do_u32 + c * (kRows * 128), &tm_do, c * 64, q_row0, SPLASH_RBAR(q_full, 0));
+      }
       int slot = 0;
       uint32_t phase = 0;
       for (int t = 0; t < total; ++t) {
         const int s = t / kSub, sb = t % kSub;
         const int j = a.block_list[sched_off + s];
         const int kv_row = kv_row0 + j * 128 + sb * BC;
-        if (t >= stages && !mbar_wait(SPLASH_RBAR(empty, slot), phase ^ 1, ctx, kRSiteTmaEmpty, t)) break;
+        if (t >= stages && !warp_wait(SPLASH_RBAR(empty, slot), phase ^ 1, ctx, kRSiteTmaEmpty, t)) break;
         const bool partial_dense = a.has_dense && a.block_kind[sched_off + s] == SPLASH_BLOCK_PARTIAL;
         const uint32_t bytes = L::kKStage + L::kVStage + (a.has_seg ? L::kVecStage : 0) +
                                (partial_dense ? L::kMaskStage : 0);
         const uint32_t bar = SPLASH_RBAR(full, slot);
-        mbar_arrive_expect_tx(bar, bytes);
+        const int mrow = partial_dense ? a.mask_block[sched_off + s] * 128 : 0;
+        if (elect_one()) {
+          mbar_arrive_expect_tx(bar, bytes);
 #pragma unroll
-        for (int c = 0; c < D / 64; ++c)
-          tma_load_2d(k_u32 + slot * L::kKStage + c * (BC * 128), &tm_k, c * 64, kv_row, bar);
+          for (int c = 0; c < D / 64; ++c)
+            tma_load_2d(k_u32 + slot * L::kKStage + c * (BC * 128), &tm_k, c * 64, kv_row, bar);
 #pragma unroll
-        for (int c = 0; c < DV / 64; ++c)
-          tma_load_2d(v_u32 + slot * L::kVStage + c * (BC * 128), &tm_v, c * 64, kv_row, bar);
-        if (a.has_seg)
-          bulk_load_1d(seg_u32 + slot * L::kVecStage, a.seg_kv + static_cast<size_t>(b) * a.kv_len + j * 128 + sb * BC,
-                       L::kVecStage, bar);
-        if (partial_dense)
-          tma_load_2d(mask_u32 + slot * L::kMaskStage, &tm_mask, sb * BC, a.mask_block[sched_off + s] * 128, bar);
+          for (int c = 0; c < DV / 64; ++c)
+            tma_load_2d(v_u32 + slot * L::kVStage + c * (BC * 128), &tm_v, c * 64, kv_row, bar);
+          if (a.has_seg)
+            bulk_load_1d(seg_u32 + slot * L::kVecStage,
+                         a.seg_kv + static_cast<size_t>(b) * a.kv_len + j * 128 + sb * BC, L::kVecStage, bar);
+          if (partial_dense) tma_load_2d(mask_u32 + slot * L::kMaskStage, &tm_mask, sb * BC, mrow, bar);
+        }
         if (++slot == stages) { slot = 0; phase ^= 1; }
       }
-    } else if (warp == kEwWarps + 1 && lane == 0 && total > 0) {
+    } else if (warp == kEwWarps + 1 && total > 0) {
       // ------------------------------- MMA issuer -------------------------------
       constexpr uint32_t kIdescScore = make_idesc(BF16, 128, BC, false, false);
       constexpr uint32_t kIdescDq = make_idesc(BF16, 128, D, false, true);
@@ -182,36 +187,36 @@ splash_bwd_row_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         const uint32_t q_lo = desc_lo(q_u32, 16), k_lo = desc_lo(k_u32 + slot * L::kKStage, 16);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          umma_ss2(tmem + L::kColS, q_lo + (((kk / 4) * (kRows * 128) + (kk % 4) * 32) >> 4), kDescHi,
+          umma_ss2_w(tmem + L::kColS, q_lo + (((kk / 4) * (kRows * 128) + (kk % 4) * 32) >> 4), kDescHi,
                    k_lo + (((kk / 4) * (BC * 128) + (kk % 4) * 32) >> 4), kDescHi, kIdescScore, kk > 0);
         const uint32_t do_lo = desc_lo(do_u32, 16), v_lo = desc_lo(v_u32 + slot * L::kVStage, 16);
 #pragma unroll
         for (int kk = 0; kk < DV / 16; ++kk)
-          umma_ss2(tmem + L::kColDp, do_lo + (((kk / 4) * (kRows * 128) + (kk % 4) * 32) >> 4), kDescHi,
+          umma_ss2_w(tmem + L::kColDp, do_lo + (((kk / 4) * (kRows * 128) + (kk % 4) * 32) >> 4), kDescHi,
                    v_lo + (((kk / 4) * (BC * 128) + (kk % 4) * 32) >> 4), kDescHi, kIdescScore, kk > 0);
       };
-      bool ok = mbar_wait(SPLASH_RBAR(q_full, 0), 0, ctx, kRSiteMmaQ, 0) &&
-                mbar_wait(SPLASH_RBAR(full, 0), 0, ctx, kRSiteMmaFull, 0);
+      bool ok = warp_wait(SPLASH_RBAR(q_full, 0), 0, ctx, kRSiteMmaQ, 0) &&
+                warp_wait(SPLASH_RBAR(full, 0), 0, ctx, kRSiteMmaFull, 0);
       if (ok) {
         tc_fence_after();
         issue_scores(0);
-        umma_commit(SPLASH_RBAR(s_ready, 0));
+        umma_commit_w(SPLASH_RBAR(s_ready, 0));
         int slot = 0;
         uint32_t phase = 0;
         for (int t = 0; t < total; ++t) {
           int slot1 = slot + 1;
           uint32_t phase1 = phase;
           if (slot1 == stages) { slot1 = 0; phase1 ^= 1; }
-          if (!mbar_wait(SPLASH_RBAR(ds_ready, 0), t & 1, ctx, kRSiteMmaDs, t)) break;
+          if (!warp_wait(SPLASH_RBAR(ds_ready, 0), t & 1, ctx, kRSiteMmaDs, t)) break;
           tc_fence_after();
           auto issue_dq = [&]() {
             // dQ += dS K  (K tile read MN-major: boxes of 64 head-dim columns, BC rows each)
             const uint32_t k_lo = desc_lo(k_u32 + slot * L::kKStage, BC * 128);
 #pragma unroll
             for (int kk = 0; kk < BC / 16; ++kk)
-              umma_ts2(tmem + L::kColDq, tmem + L::kColDs + (t & 1) * (BC / 2) + kk * 8, k_lo + ((kk * 2048) >> 4),
+              umma_ts2_w(tmem + L::kColDq, tmem + L::kColDs + (t & 1) * (BC / 2) + kk * 8, k_lo + ((kk * 2048) >> 4),
                        kDescHi, kIdescDq, (t > 0 || kk > 0) ? 1u : 0u);
-            umma_commit(SPLASH_RBAR(empty, slot));
+            umma_commit_w(SPLASH_RBAR(empty, slot));
           };
           // With a single stage the next K/V tile can only arrive once dQ has released
           // this one; with more, the next scores go first so that dQ overlaps the
@@ -219,16 +224,16 @@ splash_bwd_row_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           if (stages == 1) issue_dq();
           if (t + 1 < total) {
             // S / dP of step t have been read: the next scores may overwrite them.
-            if (!mbar_wait(SPLASH_RBAR(full, slot1), phase1, ctx, kRSiteMmaFull, t + 1)) break;
+            if (!warp_wait(SPLASH_RBAR(full, slot1), phase1, ctx, kRSiteMmaFull, t + 1)) break;
             tc_fence_after();
             issue_scores(slot1);
-            umma_commit(SPLASH_RBAR(s_ready, 0));
+            umma_commit_w(SPLASH_RBAR(s_ready, 0));
           }
           if (stages != 1) issue_dq();
           slot = slot1;
           phase = phase1;
         }
-        umma_commit(SPLASH_RBAR(acc_done, 0));
+        umma_commit_w(SPLASH_RBAR(acc_done, 0));
       }
     }
   } else {

@@ -27,6 +27,8 @@
 
 #include <stddef.h>
 
+#include <type_traits>
+
 #include "../../include/splash_sm100.h"
 #include "ptx.cuh"
 
@@ -35,6 +37,10 @@ namespace splash {
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;  // in powers of two
+#ifndef SPLASH_EMU_PAIRS
+#define SPLASH_EMU_PAIRS 0
+#endif
+constexpr int kEmuPairs = SPLASH_EMU_PAIRS;  // of every 8 element pairs, how many use the polynomial exp2
 
 struct FwdArgs {
   const int32_t* num_steps;
@@ -433,14 +439,20 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
 
         // ---- online softmax with a stale maximum --------------------------------
-        float mx0 = sv[0], mx1 = sv[1], mx2 = sv[2], mx3 = sv[3];
+        float mx0 = max3(sv[0], sv[1], sv[2]), mx1 = max3(sv[3], sv[4], sv[5]);
+        float mx2 = fmaxf(sv[6], sv[7]), mx3 = sv[8];
 #pragma unroll
-        for (int i = 4; i < BKV; i += 4) {
-          mx0 = fmaxf(mx0, sv[i]);
-          mx1 = fmaxf(mx1, sv[i + 1]);
-          mx2 = fmaxf(mx2, sv[i + 2]);
-          mx3 = fmaxf(mx3, sv[i + 3]);
+        for (int i = 9; i + 7 < BKV; i += 8) {
+          mx0 = max3(mx0, sv[i], sv[i + 1]);
+          mx1 = max3(mx1, sv[i + 2], sv[i + 3]);
+          mx2 = max3(mx2, sv[i + 4], sv[i + 5]);
+          mx3 = max3(mx3, sv[i + 6], sv[i + 7]);
         }
+        // BKV = 64 or 128: elements BKV-7 .. BKV-1 remain.
+        mx0 = max3(mx0, sv[BKV - 7], sv[BKV - 6]);
+        mx1 = max3(mx1, sv[BKV - 5], sv[BKV - 4]);
+        mx2 = max3(mx2, sv[BKV - 3], sv[BKV - 2]);
+        mx3 = fmaxf(mx3, sv[BKV - 1]);
         const float m_new = fmaxf(m_run, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
         const bool moved = (m_new - m_run) * kLog2e > kRescaleThreshold;  // false for NaN (-inf - -inf)
         float alpha = 1.f;
@@ -450,28 +462,37 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           l_run *= alpha;
         }
         const float m_scaled = (m_run == -INFINITY) ? 0.f : m_run * kLog2e;
-        float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
-        // P goes over the S it came from, 32 columns of S (16 packed words) at a time
-        // so that only one small staging group is live beside the row itself.
+        const float2 scale2 = make_float2(kLog2e, kLog2e), shift2 = make_float2(-m_scaled, -m_scaled);
+        float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
+        // P goes over the S it came from, 32 columns of S (16 packed words) at a time so
+        // that only one small staging group is live beside the row itself.  In blocks with
+        // nothing masked, kEmuPairs of every 8 element pairs take the polynomial exp2 (FMA
+        // pipe) instead of ex2.approx (special function unit), the unit this loop
+        // saturates.  The two variants are separate straight-line loops on purpose.
+        auto exp_row = [&](auto emu_tag) {
+          constexpr int kEmu = decltype(emu_tag)::value;
 #pragma unroll
-        for (int c = 0; c < BKV / 32; ++c) {
-          uint32_t pk[16];
+          for (int c = 0; c < BKV / 32; ++c) {
+            uint32_t pk[16];
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            const float p0 = ex2_approx(fmaf(sv[c * 32 + i], kLog2e, -m_scaled));
-            const float p1 = ex2_approx(fmaf(sv[c * 32 + i + 1], kLog2e, -m_scaled));
-            const float p2 = ex2_approx(fmaf(sv[c * 32 + i + 2], kLog2e, -m_scaled));
-            const float p3 = ex2_approx(fmaf(sv[c * 32 + i + 3], kLog2e, -m_scaled));
-            sum0 += p0;
-            sum1 += p1;
-            sum2 += p2;
-            sum3 += p3;
-            pk[i / 2] = pack2<BF16>(p0, p1);
-            pk[i / 2 + 1] = pack2<BF16>(p2, p3);
+            for (int j = 0; j < 16; ++j) {
+              const float2 x = fma2(make_float2(sv[c * 32 + 2 * j], sv[c * 32 + 2 * j + 1]), scale2, shift2);
+              float2 pr;
+              if ((j & 7) >= 8 - kEmu) {
+                pr = ex2_poly2(x);
+              } else {
+                pr.x = ex2_approx(x.x);
+                pr.y = ex2_approx(x.y);
+              }
+              if (j & 1) sum_b = add2(sum_b, pr); else sum_a = add2(sum_a, pr);
+              pk[j] = pack2<BF16>(pr.x, pr.y);
+            }
+            tmem_st16(s_tmem + c * 16, pk);
           }
-          tmem_st16(s_tmem + c * 16, pk);
-        }
-        l_run += (sum0 + sum1) + (sum2 + sum3);
+        };
+        if (kEmuPairs > 0 && !partial && !a.has_seg) exp_row(std::integral_constant<int, kEmuPairs>{});
+        else exp_row(std::integral_constant<int, 0>{});
+        l_run += (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
 
         // O may only be touched once P.V of the previous step has finished.  With two
         // tiles the s_ready wait above already certifies that (the tensor core runs

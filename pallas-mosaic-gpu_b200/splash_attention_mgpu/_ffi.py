@@ -13,7 +13,8 @@ from ctypes import (POINTER, Structure, c_char_p, c_float, c_int, c_int32,
                     c_int64, c_void_p)
 
 LIB_NAME = "libsplash_sm100.so"
-LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), LIB_NAME)
+# SPLASH_LIB_PATH points at an alternative build of the same library (e.g. a tuning build).
+LIB_PATH = os.environ.get("SPLASH_LIB_PATH") or os.path.join(os.path.dirname(os.path.abspath(__file__)), LIB_NAME)
 
 SPLASH_OK = 0
 SPLASH_INVALID_ARGUMENT = -1
