@@ -19,7 +19,7 @@
 //     stages dS^T in shared memory
 //   dV  += P^T dO       TMEM x smem
 //   dK  += dS^T Q       TMEM x smem
-//   dQ^T = K^T dS^T     smem x smem (FUSED), written over the dead S^T columns and
+//   dQ^T = K^T dS^T     smem x smem (FUSED), written over the dead dP^T columns and
 //                       drained by a writer warpgroup
 //
 // S^T and dP^T are double-buffered in tensor memory: the scores of step t+2 are issued
@@ -56,6 +56,7 @@ struct BwdArgs {
   int32_t batch, heads, kv_heads, q_len, kv_len;
   int32_t mask_heads, max_steps, q_blocks, kv_blocks, stages;
   int32_t has_dense, has_seg;
+  int32_t head_group;  // heads whose blocks are interleaved in the launch order
   float mask_value, soft_cap;
 };
 
@@ -81,7 +82,7 @@ struct ColLayout {
   static constexpr int kDsStage = kRows * BC * 2;   // FUSED: dS^T as an MMA operand
   static constexpr int kDqStage = 128 * 32 * 4;     // FUSED: half a dQ^T tile (32 q columns), f32
   // Tensor memory columns: two S^T buffers, two dP^T buffers, dK, dV.  P^T lives in the
-  // S^T buffer it came from, dS^T in the dP^T buffer, dQ^T reuses the S^T buffer.
+  // S^T buffer it came from, dS^T in the dP^T buffer, dQ^T reuses the dP^T buffer.
   static constexpr int kColS = 0, kColDp = 2 * BC, kColDk = 4 * BC, kColDv = 4 * BC + D;
   static constexpr int kTmemUsed = 4 * BC + 2 * D;
   static constexpr int kTmemCols = 512;
@@ -196,9 +197,8 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 
   // ---- which KV block ----------------------------------------------------------
   const int group = a.heads / a.kv_heads;
-  const int hb_count = a.kv_heads * a.batch;
-  const int order_idx = blockIdx.x / hb_count;
-  const int hb = blockIdx.x - order_idx * hb_count;
+  int hb, order_idx;
+  decode_work_item(blockIdx.x, a.kv_blocks, a.kv_heads * a.batch, a.head_group, hb, order_idx);
   const int kvh = hb % a.kv_heads;
   const int b = hb / a.kv_heads;
   const int head0 = kvh * group;
@@ -327,48 +327,58 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           const int buf = t & 1;
           if (!warp_wait(SPLASH_CBAR(p_ready, buf), (t >> 1) & 1, ctx, kBSiteMmaP, t)) break;
           tc_fence_after();
+          // A operands of dK / dV are the packed 16-bit values the elementwise warps wrote
+          // over dP^T / S^T: keys 0-31 sit in columns 0-15 of the buffer, keys 32-63 in
+          // columns 32-47 (each warpgroup packs into its own half).  B operands MN-major:
+          // boxes of 64 columns, BC rows each.
           {
-            // dV += P^T dO ; dK += dS^T Q.  A operands are the packed 16-bit values the
-            // elementwise warps wrote over S^T / dP^T: keys 0-31 sit in columns 0-15 of the
-            // buffer, keys 32-63 in columns 32-47 (each warpgroup packs into its own half).
-            // B operands MN-major: boxes of 64 columns, BC rows each.
-            const uint32_t do_lo = desc_lo(do_u32 + c_slot * L::kDoStage, BC * 128);
+            // dK += dS^T Q
             const uint32_t q_lo = desc_lo(q_u32 + c_slot * L::kQStage, BC * 128);
-#pragma unroll
-            for (int kk = 0; kk < BC / 16; ++kk)
-              umma_ts2_w(tmem + L::kColDv, tmem + L::kColS + buf * BC + (kk >> 1) * 32 + (kk & 1) * 8,
-                         do_lo + ((kk * 2048) >> 4), kDescHi, kIdescAcc, (t > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
             for (int kk = 0; kk < BC / 16; ++kk)
               umma_ts2_w(tmem + L::kColDk, tmem + L::kColDp + buf * BC + (kk >> 1) * 32 + (kk & 1) * 8,
                          q_lo + ((kk * 2048) >> 4), kDescHi, kIdescAcc, (t > 0 || kk > 0) ? 1u : 0u);
           }
-          umma_commit_w(SPLASH_CBAR(empty, c_slot));
           if constexpr (FUSED) {
             // dQ^T[d, q] = sum_kv K[kv, d] dS^T[kv, q]: A = K read MN-major, B = staged dS^T
-            // MN-major.  The result replaces S^T / P^T of this step, which dV has consumed
-            // (the tensor core runs its instructions in issue order).
+            // MN-major.  The result replaces dP^T / dS^T of this step, which dK has consumed
+            // (the tensor core runs its instructions in issue order).  It is issued this
+            // early so that the writer has drained it long before the next dP^T needs the
+            // columns.
             const uint32_t k_lo = desc_lo(k_u32, kRows * 128);
             const uint32_t ds_lo = desc_lo(ds_u32 + buf * L::kDsStage, kRows * 128);
 #pragma unroll
             for (int kk = 0; kk < kRows / 16; ++kk)
-              umma_ss2_w(tmem + L::kColS + buf * BC, k_lo + ((kk * 2048) >> 4), kDescHi, ds_lo + ((kk * 2048) >> 4),
+              umma_ss2_w(tmem + L::kColDp + buf * BC, k_lo + ((kk * 2048) >> 4), kDescHi, ds_lo + ((kk * 2048) >> 4),
                          kDescHi, kIdescDq, kk > 0);
             umma_commit_w(SPLASH_CBAR(dq_ready, 0));
           }
+          {
+            // dV += P^T dO
+            const uint32_t do_lo = desc_lo(do_u32 + c_slot * L::kDoStage, BC * 128);
+#pragma unroll
+            for (int kk = 0; kk < BC / 16; ++kk)
+              umma_ts2_w(tmem + L::kColDv, tmem + L::kColS + buf * BC + (kk >> 1) * 32 + (kk & 1) * 8,
+                         do_lo + ((kk * 2048) >> 4), kDescHi, kIdescAcc, (t > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit_w(SPLASH_CBAR(empty, c_slot));
           if (t + 2 < total) {
             // Scores of step t+2 go into the buffers step t has just vacated.
             if (!warp_wait(SPLASH_CBAR(full, s_slot), s_phase, ctx, kBSiteMmaFull, t + 2)) break;
             tc_fence_after();
-            issue_dp(s_slot, buf);
+            issue_s(s_slot, buf);
             if constexpr (FUSED) {
-              // The writer must have taken dQ^T of step t out of the S^T buffer.
+              // The writer must have taken dQ^T of step t out of the dP^T buffer.
               if (!warp_wait(SPLASH_CBAR(dq_free, 0), t & 1, ctx, kBSiteMmaDqFree, t)) break;
               tc_fence_after();
             }
-            issue_s(s_slot, buf);
+            issue_dp(s_slot, buf);
             umma_commit_w(SPLASH_CBAR(s_ready, buf));
             if (++s_slot == stages) { s_slot = 0; s_phase ^= 1; }
+          } else if constexpr (FUSED) {
+            // Tail steps: still observe every phase of dq_free, so that dq_ready never
+            // runs two phases ahead of the writer.
+            if (!warp_wait(SPLASH_CBAR(dq_free, 0), t & 1, ctx, kBSiteMmaDqFree, t)) break;
           }
           if (++c_slot == stages) c_slot = 0;
         }
@@ -380,7 +390,7 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     if constexpr (FUSED) {
       const int wq = warp & 3;
       const int drow = wq * 32 + lane;  // head-dim index = TMEM lane
-      const uint32_t dq_tmem = tmem + (static_cast<uint32_t>(wq * 32) << 16) + L::kColS;
+      const uint32_t dq_tmem = tmem + (static_cast<uint32_t>(wq * 32) << 16) + L::kColDp;
       const bool leader = (warp == kWriterWarp0 && lane == 0);
       bool alive = true;
       int t = 0;

@@ -34,6 +34,7 @@ inline void fill_bwd_args(BwdArgs& a, const SplashParams& p, bool dense, bool se
   a.stages = p.num_stages;
   a.has_dense = dense;
   a.has_seg = seg;
+  a.head_group = 4;
   a.mask_value = p.mask_value;
   a.soft_cap = p.soft_cap;
 }

@@ -96,9 +96,8 @@ splash_bwd_row_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const int warp = uniform_warp_index();
   const int lane = threadIdx.x & 31;
 
-  const int hb_count = a.heads * a.batch;
-  const int order_idx = blockIdx.x / hb_count;
-  const int hb = blockIdx.x - order_idx * hb_count;
+  int hb, order_idx;
+  decode_work_item(blockIdx.x, a.q_blocks, a.heads * a.batch, a.head_group, hb, order_idx);
   const int h = hb % a.heads;
   const int b = hb / a.heads;
   const int mh = a.mask_heads > 1 ? h : 0;

@@ -57,6 +57,7 @@ struct FwdArgs {
   int32_t batch, heads, kv_heads, q_len, kv_len;
   int32_t mask_heads, max_steps, q_blocks, stages;
   int32_t has_dense, has_seg;
+  int32_t head_group;  // heads whose blocks are interleaved in the launch order
   float mask_value, soft_cap;
 };
 
@@ -139,9 +140,8 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const int lane = threadIdx.x & 31;
 
   // ---- which tile of work ---------------------------------------------------
-  const int hb_count = a.heads * a.batch;
-  const int order_idx = blockIdx.x / hb_count;  // heaviest q blocks of every head first
-  const int hb = blockIdx.x - order_idx * hb_count;
+  int hb, order_idx;
+  decode_work_item(blockIdx.x, a.q_blocks, a.heads * a.batch, a.head_group, hb, order_idx);
   const int h = hb % a.heads;
   const int b = hb / a.heads;
   const int mh = a.mask_heads > 1 ? h : 0;

@@ -62,6 +62,7 @@ int launch_fwd_typed(const SplashParams& p, cudaStream_t stream) {
   a.stages = p.num_stages;
   a.has_dense = dense;
   a.has_seg = seg;
+  a.head_group = 8;
   a.mask_value = p.mask_value;
   a.soft_cap = p.soft_cap;
 

@@ -335,6 +335,22 @@ __device__ __forceinline__ void umma_commit_w(uint32_t bar) {
       : "memory");
 }
 
+// Launch order of the (head, block) work items of a grid.  Heads are taken in groups of
+// `group` (the last group may be smaller); inside a group the blocks of all its heads
+// are interleaved in order position, i.e. heaviest blocks of every head first.  CTAs
+// that run at the same time therefore belong to few heads (their K/V or Q/dO tiles
+// stay in L2) while the tail of each group still consists of the lightest blocks.
+__device__ __forceinline__ void decode_work_item(int bid, int blocks, int num_heads, int group, int& head,
+                                                 int& order_idx) {
+  const int per_group = group * blocks;
+  const int grp = bid / per_group;
+  const int first = grp * group;
+  const int size = min(group, num_heads - first);
+  const int r = bid - grp * per_group;
+  order_idx = r / size;
+  head = first + (r - order_idx * size);
+}
+
 // Warp index that the compiler can prove to be warp-uniform (a value read from lane 0).
 __device__ __forceinline__ int uniform_warp_index() {
   return __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
