@@ -311,12 +311,18 @@ def run_ours(args):
     bwd_tflops = (fb_flops - fwd_flops) / (bwd_ms * 1e-3) / 1e12
     # Dominant launch group: the backward call (delta pre-pass, accumulator clear, fused
     # kernel, transpose-cast); its algorithmic work is 2.5x the forward FLOPs.
+    # `traffic`: dram__bytes_read + dram__bytes_write of that kernel from the committed ncu
+    # capture of this same workload (profiles/ncu_*_causal_s8192_d128.md), bytes per launch.
+    default_wl = workload == DEFAULT_WORKLOAD
     roofline = dict(bound="tensor", achieved=bwd_tflops, peak=peaks["sustained"], unit="TFLOP/s",
-                    frac=bwd_tflops / peaks["sustained"], traffic=None, peak_source=peaks["source"] + " sustained bf16",
-                    kernel="splash_bwd_col_kernel<128,128,64,fused> (+delta, clear, transpose-cast)",
+                    frac=bwd_tflops / peaks["sustained"], traffic=630.6e6 if default_wl else None,
+                    peak_source=peaks["source"] + " sustained bf16",
+                    kernel="splash_bwd_col_kernel<128,fused> (93% of the backward launch group; timed with its "
+                           "delta pre-pass, accumulator clear and transpose-cast)" if d == 128 else
+                           "splash_bwd_row_kernel + splash_bwd_col_kernel (+delta)",
                     frac_of_nominal_2250=bwd_tflops / 2250.0)
     roofline_fwd = dict(bound="tensor", achieved=fwd_tflops, peak=peaks["sustained"], unit="TFLOP/s",
-                        frac=fwd_tflops / peaks["sustained"], traffic=None,
+                        frac=fwd_tflops / peaks["sustained"], traffic=251.2e6 if default_wl else None,
                         kernel=f"splash_fwd_kernel<block_q={bs.block_q},block_kv={bs.block_kv}>",
                         frac_of_nominal_2250=fwd_tflops / 2250.0)
     cpu = None
