@@ -166,8 +166,11 @@ class SplashAttentionKernel:
     self.interpret = interpret
     self._infos: dict = {}
     self._device_schedules: dict = {}
-    # 128x128 schedule: backward kernels and FLOP accounting.
-    self.info = self.fwd_info(128, 128)
+
+  @property
+  def info(self) -> mask_info_lib.GpuMaskInfo:
+    """128x128 schedule: backward kernels and FLOP accounting (built on first use)."""
+    return self.fwd_info(128, 128)
 
   def fwd_info(self, block_q: int, block_kv: int) -> mask_info_lib.GpuMaskInfo:
     key = (block_q, block_kv)
