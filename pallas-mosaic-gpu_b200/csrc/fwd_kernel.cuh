@@ -64,24 +64,37 @@ struct FwdArgs {
 // Wait sites, reported in the status word when a wait runs out.
 enum FwdSite : int {
   kSiteTmaKEmpty = 1, kSiteTmaVEmpty, kSiteTmaAuxEmpty,
-  kSiteMmaQ, kSiteMmaK, kSiteMmaV, kSiteMmaP,
-  kSiteSmxS, kSiteSmxAux, kSiteSmxPv, kSiteSmxDone, kSiteSmxEpi,
+  kSiteMmaQ, kSiteMmaK, kSiteMmaV, kSiteMmaP, kSiteMmaSFree,
+  kSiteSmxS, kSiteSmxAux, kSiteSmxPv, kSiteSmxDone, kSiteSmxEpi, kSiteSmxM, kSiteSmxFin,
 };
 
-template <int D, int DV, int BKV, int NT>
+// AW softmax warpgroups take the KV steps of a tile in turn (one-tile kernel only).
+template <int D, int DV, int BKV, int NT, int AW = 1>
 struct FwdLayout {
+  static_assert(AW == 1 || (AW == 2 && NT == 1), "alternating warpgroups need the one-tile kernel");
   static constexpr int kTile = 128;
   static constexpr int kQBytes = NT * kTile * D * 2;
   static constexpr int kKStage = BKV * D * 2;
   static constexpr int kVStage = BKV * DV * 2;
   static constexpr int kMaskStage = NT * kTile * BKV;
   static constexpr int kSegStage = BKV * 4;
-  static constexpr int kTmemUsed = 2 * BKV + NT * DV;
+  // Tensor-memory columns: S (two buffers) | P when it has columns of its own | O.
+  // P lies over its S except with alternating warpgroups, where freeing S(t) as soon as
+  // it has been read lets the scores of step t + 2 run under the softmax of step t.
+  static constexpr int kPCol = AW == 2 ? 2 * BKV : 0;     // first column of P buffer 0
+  static constexpr int kPStride = AW == 2 ? BKV / 2 : BKV;  // from P buffer 0 to buffer 1
+  static constexpr int kOCol = AW == 2 ? 3 * BKV : 2 * BKV;
+  static constexpr int kTmemUsed = kOCol + NT * DV;
   static constexpr int kTmemCols = kTmemUsed <= 128 ? 128 : (kTmemUsed <= 256 ? 256 : 512);
-  static constexpr int kThreads = (NT + 1) * 128;
+  static_assert(kTmemUsed <= 512, "tensor memory has 512 columns");
+  static constexpr int kSoftmaxGroups = NT * AW;
+  static constexpr int kThreads = (kSoftmaxGroups + 1) * 128;
+  // Row maxima shared by the alternating warpgroups, and their partial row sums.
+  static constexpr int kShareBytes = AW > 1 ? 3 * kTile * 4 : 0;
   static constexpr bool kOStageInQ = (NT == 2) || (DV <= D);
-  // Register split between the warpgroups of the two-tile kernel (multiples of 8;
-  // 2 * 128 * softmax + 128 * producer <= 64K).
+  // Register split between the warpgroups when there are two softmax warpgroups
+  // (multiples of 8; 2 * 128 * softmax + 128 * producer <= 64K).
+  static constexpr bool kSplitRegs = kSoftmaxGroups == 2;
   static constexpr int kSoftmaxRegs = 216;
   static constexpr int kProducerRegs = 72;
 
@@ -91,6 +104,7 @@ struct FwdLayout {
     if (dense) b += static_cast<size_t>(stages) * kMaskStage;
     if (seg) b += static_cast<size_t>(stages) * kSegStage;
     b += 1024;  // barriers, TMEM slot, flags
+    b += kShareBytes;
     return b;
   }
 };
@@ -103,8 +117,11 @@ struct FwdBarriers {
   uint64_t v_full[kFwdMaxStages], v_empty[kFwdMaxStages];
   uint64_t aux_full[kFwdMaxStages], aux_empty[kFwdMaxStages];
   uint64_t s_ready[2], p_ready[2];
-  uint64_t pv_done, o_done;
+  uint64_t pv_done[2], o_done;  // pv_done by step parity: a waiter meets every phase of a barrier in turn
   uint64_t epi[2];
+  uint64_t s_free[2];   // alternating warpgroups: S buffer read into registers
+  uint64_t m_ready[2];  // alternating warpgroups: the row maxima after step s stand in shared memory
+  uint64_t fin;         // alternating warpgroups: partial row sums posted
   uint32_t tmem_base;
   uint32_t abort_flag;
   uint32_t dead;  // status word was already non-zero at entry
@@ -113,15 +130,15 @@ struct FwdBarriers {
 #define SPLASH_BAR(field, idx) \
   (bars_u32 + static_cast<uint32_t>(offsetof(FwdBarriers, field)) + 8u * static_cast<uint32_t>(idx))
 
-template <int D, int DV, int BKV, int NT, bool BF16>
-__global__ void __launch_bounds__((NT + 1) * 128, 1)
+template <int D, int DV, int BKV, int NT, int AW, bool BF16>
+__global__ void __launch_bounds__((NT * AW + 1) * 128, 1)
 splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                   const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
                   const __grid_constant__ CUtensorMap tm_mask, const FwdArgs a) {
-  using L = FwdLayout<D, DV, BKV, NT>;
+  using L = FwdLayout<D, DV, BKV, NT, AW>;
   constexpr int kTile = 128;
   constexpr int kBq = NT * kTile;
-  constexpr int kSoftmaxWarps = 4 * NT;
+  constexpr int kSoftmaxWarps = 4 * NT * AW;
 
   extern __shared__ uint8_t smem_raw[];
   const int stages = a.stages;
@@ -132,6 +149,7 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const uint32_t mask_u32 = v_u32 + stages * L::kVStage;
   const uint32_t seg_u32 = mask_u32 + (a.has_dense ? stages * L::kMaskStage : 0);
   const uint32_t bars_u32 = seg_u32 + (a.has_seg ? stages * L::kSegStage : 0);
+  const uint32_t share_u32 = bars_u32 + 1024;  // [row maxima | partial sums of group 0 | of group 1]
   const uint32_t abort_u32 = bars_u32 + static_cast<uint32_t>(offsetof(FwdBarriers, abort_flag));
   const uint32_t dead_u32 = bars_u32 + static_cast<uint32_t>(offsetof(FwdBarriers, dead));
   const uint32_t tmem_slot_u32 = bars_u32 + static_cast<uint32_t>(offsetof(FwdBarriers, tmem_base));
@@ -162,14 +180,18 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       mbar_init(SPLASH_BAR(v_full, i), 1);
       mbar_init(SPLASH_BAR(v_empty, i), 1);
       mbar_init(SPLASH_BAR(aux_full, i), 1);
-      mbar_init(SPLASH_BAR(aux_empty, i), kSoftmaxWarps);
+      mbar_init(SPLASH_BAR(aux_empty, i), 4 * NT);  // the warps that consume one step
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(SPLASH_BAR(s_ready, i), 1);
       mbar_init(SPLASH_BAR(p_ready, i), kTile);
-      mbar_init(SPLASH_BAR(epi, i), kTile);
+      mbar_init(SPLASH_BAR(epi, i), kTile * AW);
+      mbar_init(SPLASH_BAR(m_ready, i), kTile);
+      mbar_init(SPLASH_BAR(s_free, i), kTile);
     }
+    mbar_init(SPLASH_BAR(fin, 0), kTile * AW);
     mbar_init(SPLASH_BAR(pv_done, 0), 1);
+    mbar_init(SPLASH_BAR(pv_done, 1), 1);
     mbar_init(SPLASH_BAR(o_done, 0), 1);
     fence_mbar_init();
     fence_proxy_async_smem();
@@ -192,7 +214,7 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
   if (warp >= kSoftmaxWarps) {
     // =========================== producer warpgroup ============================
-    if constexpr (NT == 2) setmaxnreg_dec<L::kProducerRegs>();
+    if constexpr (L::kSplitRegs) setmaxnreg_dec<L::kProducerRegs>();
     if (warp == kSoftmaxWarps && n > 0) {
       // ------------------------------ TMA producer ------------------------------
       // The whole warp runs the loop (warp-uniform control flow); one elected lane
@@ -201,7 +223,6 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       if (elect_one()) {
         prefetch_tensormap(&tm_q);
         prefetch_tensormap(&tm_k);
-        prefetch_tensormap(&tm_v);
         mbar_arrive_expect_tx(SPLASH_BAR(q_full, 0), L::kQBytes);
 #pragma unroll
         for (int t = 0; t < NT; ++t)
@@ -224,13 +245,6 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           for (int c = 0; c < D / 64; ++c)
             tma_load_2d(k_u32 + slot * L::kKStage + c * (BKV * 128), &tm_k, c * 64, kv_row, SPLASH_BAR(k_full, slot));
         }
-        if (s >= stages && !warp_wait(SPLASH_BAR(v_empty, slot), phase ^ 1, ctx, kSiteTmaVEmpty, s)) break;
-        if (elect_one()) {
-          mbar_arrive_expect_tx(SPLASH_BAR(v_full, slot), L::kVStage);
-#pragma unroll
-          for (int c = 0; c < DV / 64; ++c)
-            tma_load_2d(v_u32 + slot * L::kVStage + c * (BKV * 128), &tm_v, c * 64, kv_row, SPLASH_BAR(v_full, slot));
-        }
         if (has_aux) {
           if (s >= stages && !warp_wait(SPLASH_BAR(aux_empty, slot), phase ^ 1, ctx, kSiteTmaAuxEmpty, s)) break;
           const bool partial_dense = a.has_dense && a.block_kind[sched_off + s] == SPLASH_BLOCK_PARTIAL;
@@ -248,6 +262,25 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                             SPLASH_BAR(aux_full, slot));
             }
           }
+        }
+        if (++slot == stages) { slot = 0; phase ^= 1; }
+      }
+    } else if (warp == kSoftmaxWarps + 2 && n > 0) {
+      // ------------------------------ V producer --------------------------------
+      // A warp of its own, so that a V slot still held by P.V never delays the K
+      // blocks behind it, which the tensor core needs first.
+      const int kv_row0 = (b * a.kv_heads + h / (a.heads / a.kv_heads)) * a.kv_len;
+      if (elect_one()) prefetch_tensormap(&tm_v);
+      int slot = 0;
+      uint32_t phase = 0;
+      for (int s = 0; s < n; ++s) {
+        const int kv_row = kv_row0 + a.block_list[sched_off + s] * BKV;
+        if (s >= stages && !warp_wait(SPLASH_BAR(v_empty, slot), phase ^ 1, ctx, kSiteTmaVEmpty, s)) break;
+        if (elect_one()) {
+          mbar_arrive_expect_tx(SPLASH_BAR(v_full, slot), L::kVStage);
+#pragma unroll
+          for (int c = 0; c < DV / 64; ++c)
+            tma_load_2d(v_u32 + slot * L::kVStage + c * (BKV * 128), &tm_v, c * 64, kv_row, SPLASH_BAR(v_full, slot));
         }
         if (++slot == stages) { slot = 0; phase ^= 1; }
       }
@@ -270,7 +303,7 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const uint32_t b_lo = desc_lo(v_u32 + vslot * L::kVStage, BKV * 128);
 #pragma unroll
         for (int kk = 0; kk < BKV / 16; ++kk)
-          umma_ts2_w(tmem + 2 * BKV + t * DV, p_src + kk * 8, b_lo + ((kk * 2048) >> 4), kDescHi, kIdescPV,
+          umma_ts2_w(tmem + L::kOCol + t * DV, p_src + kk * 8, b_lo + ((kk * 2048) >> 4), kDescHi, kIdescPV,
                    kk > 0 ? 1u : acc);
       };
       bool ok = warp_wait(SPLASH_BAR(q_full, 0), 0, ctx, kSiteMmaQ, 0) &&
@@ -286,6 +319,42 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         umma_commit_w(SPLASH_BAR(k_empty, 0));
         int slot = 0;
         uint32_t phase = 0;
+        if constexpr (AW == 2) {
+          // The scores run two steps ahead of P.V: S(s + 2) goes into the buffer that the
+          // softmax of step s has read into registers, under that softmax.
+          int ks = 1;  // K ring position of the next scores to issue (stages >= 2)
+          uint32_t kp = 0;
+          if (n > 1) {
+            ok = warp_wait(SPLASH_BAR(k_full, ks), kp, ctx, kSiteMmaK, 1);
+            if (ok) {
+              tc_fence_after();
+              issue_qk(0, ks, tmem + BKV);
+              umma_commit_w(SPLASH_BAR(s_ready, 1));
+              umma_commit_w(SPLASH_BAR(k_empty, ks));
+              if (++ks == stages) { ks = 0; kp ^= 1; }
+            }
+          }
+          for (int s = 0; s < n && ok; ++s) {
+            const int cur = s & 1;
+            const uint32_t par = (s >> 1) & 1;
+            if (s + 2 < n) {
+              if (!warp_wait(SPLASH_BAR(k_full, ks), kp, ctx, kSiteMmaK, s + 2)) break;
+              if (!warp_wait(SPLASH_BAR(s_free, cur), par, ctx, kSiteMmaSFree, s)) break;
+              tc_fence_after();
+              issue_qk(0, ks, tmem + cur * BKV);
+              umma_commit_w(SPLASH_BAR(s_ready, cur));
+              umma_commit_w(SPLASH_BAR(k_empty, ks));
+              if (++ks == stages) { ks = 0; kp ^= 1; }
+            }
+            if (!warp_wait(SPLASH_BAR(v_full, slot), phase, ctx, kSiteMmaV, s)) break;
+            if (!warp_wait(SPLASH_BAR(p_ready, cur), par, ctx, kSiteMmaP, s)) break;
+            tc_fence_after();
+            issue_pv(0, slot, tmem + L::kPCol + cur * L::kPStride, s > 0);
+            umma_commit_w(SPLASH_BAR(v_empty, slot));
+            umma_commit_w(SPLASH_BAR(pv_done, cur));
+            if (++slot == stages) { slot = 0; phase ^= 1; }
+          }
+        } else
         for (int s = 0; s < n; ++s) {
           int slot1 = slot + 1;
           uint32_t phase1 = phase;
@@ -305,7 +374,7 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             tc_fence_after();
             issue_pv(0, slot, tmem + cur * BKV, s > 0);
             umma_commit_w(SPLASH_BAR(v_empty, slot));
-            umma_commit_w(SPLASH_BAR(pv_done, 0));
+            umma_commit_w(SPLASH_BAR(pv_done, cur));
           } else {
             if (!warp_wait(SPLASH_BAR(v_full, slot), phase, ctx, kSiteMmaV, s)) break;
             if (!warp_wait(SPLASH_BAR(p_ready, 0), s & 1, ctx, kSiteMmaP, s)) break;
@@ -335,22 +404,31 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     }
   } else {
     // ============================ softmax warpgroups ============================
-    if constexpr (NT == 2) setmaxnreg_inc<L::kSoftmaxRegs>();
-    const int t = warp >> 2;                       // which q tile
+    if constexpr (L::kSplitRegs) setmaxnreg_inc<L::kSoftmaxRegs>();
+    // Two tiles: warpgroup g owns tile g.  One tile with AW warpgroups: group g takes the
+    // KV steps g, g + AW, ... of the tile, so that AW steps are in the softmax at a time;
+    // the groups pass the (stale) row maxima to one another through shared memory, keep
+    // partial row sums, and split the columns of O in the epilogue.
+    const int grp = warp >> 2;
+    const int t = (NT == 2) ? grp : 0;             // which q tile
     const int row = (warp & 3) * 32 + lane;        // row inside the tile
     const int q_pos = qi * kBq + t * kTile + row;  // position in the sequence
     // TMEM address of this thread's lane quarter, column 0.
     const uint32_t tmem_row = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
-    const uint32_t o_tmem = tmem_row + 2 * BKV + t * DV;
+    const uint32_t o_tmem = tmem_row + L::kOCol + t * DV;
+    const uint32_t m_sh = share_u32 + row * 4;                    // the row's maximum after the latest step
+    const uint32_t l_sh = share_u32 + (1 + grp) * kTile * 4 + row * 4;  // this group's partial row sum
+    constexpr int kEpiCols = DV / AW;                             // columns of O per thread in the epilogue
+    const int epi_col0 = (AW == 2) ? grp * kEpiCols : 0;
 
     if (n == 0) {
       // No visible block: zeros and lse = mask_value, nothing else runs.
       const size_t out_row = static_cast<size_t>(q_row0) + t * kTile + row;
       const uint4 z = make_uint4(0, 0, 0, 0);
-      uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(a.out) + out_row * (DV * 2));
+      uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(a.out) + out_row * (DV * 2)) + epi_col0 * 2 / 16;
 #pragma unroll
-      for (int c = 0; c < DV * 2 / 16; ++c) dst[c] = z;
-      if (a.lse_out) a.lse_out[out_row] = a.mask_value;
+      for (int c = 0; c < kEpiCols * 2 / 16; ++c) dst[c] = z;
+      if (a.lse_out && epi_col0 == 0) a.lse_out[out_row] = a.mask_value;
     } else {
       // Per-row band in units of (kv_pos - q_pos); a chunk restriction folds in.
       int band_lo = -(1 << 30), band_hi = (1 << 30);
@@ -368,29 +446,37 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
       float m_run = -INFINITY;  // stale running max, raw logit units
       float l_run = 0.f;
-      int slot = 0;
-      uint32_t phase = 0;
-      int kind = a.block_kind[sched_off];
-      int jblk = a.block_list[sched_off];
+      const int s_first = (AW == 2) ? grp : 0;
+      int slot = s_first % stages;
+      uint32_t phase = (s_first / stages) & 1;
+      int kind = s_first < n ? a.block_kind[sched_off + s_first] : 0;
+      int jblk = s_first < n ? a.block_list[sched_off + s_first] : 0;
       bool alive = true;
+      float sv[BKV];  // the current row of S
+      auto load_row = [&](int buf, uint32_t par, int step) {
+        if (!warp_wait(SPLASH_BAR(s_ready, buf), par, ctx, kSiteSmxS, step)) return false;
+        tc_fence_after();
+        uint32_t* raw = reinterpret_cast<uint32_t*>(sv);
+#pragma unroll
+        for (int c = 0; c < BKV / 32; ++c) tmem_ld32(tmem_row + buf * BKV + c * 32, raw + c * 32);
+        return true;
+      };
 
-      for (int s = 0; s < n; ++s) {
+      for (int s = s_first; s < n; s += AW) {
         const int kind_now = kind, j_now = jblk;
-        if (s + 1 < n) {
-          kind = a.block_kind[sched_off + s + 1];
-          jblk = a.block_list[sched_off + s + 1];
+        if (s + AW < n) {
+          kind = a.block_kind[sched_off + s + AW];
+          jblk = a.block_list[sched_off + s + AW];
         }
         const int buf = (NT == 2) ? t : (s & 1);
         const uint32_t par = (NT == 2) ? (s & 1) : ((s >> 1) & 1);
-        const uint32_t s_tmem = tmem_row + buf * BKV;
-        if (!warp_wait(SPLASH_BAR(s_ready, buf), par, ctx, kSiteSmxS, s)) { alive = false; break; }
-        tc_fence_after();
-        float sv[BKV];
-        {
-          uint32_t* raw = reinterpret_cast<uint32_t*>(sv);
-#pragma unroll
-          for (int c = 0; c < BKV / 32; ++c) tmem_ld32(s_tmem + c * 32, raw + c * 32);
-          tmem_wait_ld();
+        const uint32_t p_tmem = tmem_row + L::kPCol + buf * L::kPStride;
+        if (!load_row(buf, par, s)) { alive = false; break; }
+        tmem_wait_ld();
+        if constexpr (AW == 2) {
+          // The row is in registers: the tensor core may write the scores of step s + 2.
+          tc_fence_before();
+          mbar_arrive(SPLASH_BAR(s_free, buf));
         }
         if (a.soft_cap > 0.f) {
           const float cap = a.soft_cap, inv_cap = 1.f / a.soft_cap;
@@ -453,6 +539,18 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         mx1 = max3(mx1, sv[BKV - 5], sv[BKV - 4]);
         mx2 = max3(mx2, sv[BKV - 3], sv[BKV - 2]);
         mx3 = fmaxf(mx3, sv[BKV - 1]);
+        if constexpr (AW == 2) {
+          // The maximum the previous step settled on (the other group's); this group's
+          // partial sum moves to that scale first.
+          if (s > 0) {
+            if (!warp_wait(SPLASH_BAR(m_ready, (s - 1) & 1), ((s - 1) >> 1) & 1, ctx, kSiteSmxM, s)) { alive = false; break; }
+            const float m_prev = __uint_as_float(lds32(m_sh));
+            if (m_prev != m_run) {
+              l_run = (m_run == -INFINITY) ? 0.f : l_run * ex2_approx((m_run - m_prev) * kLog2e);
+              m_run = m_prev;
+            }
+          }
+        }
         const float m_new = fmaxf(m_run, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
         const bool moved = (m_new - m_run) * kLog2e > kRescaleThreshold;  // false for NaN (-inf - -inf)
         float alpha = 1.f;
@@ -460,6 +558,14 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           alpha = ex2_approx((m_run - m_new) * kLog2e);  // 0 when m_run was -inf
           m_run = m_new;
           l_run *= alpha;
+        }
+        if constexpr (AW == 2) {
+          if (moved || s == 0) sts32(m_sh, __float_as_uint(m_run));
+          mbar_arrive(SPLASH_BAR(m_ready, s & 1));
+        }
+        if constexpr (AW == 2) {
+          // P has its own columns: they are free once P.V of this group's previous step is done.
+          if (s >= 2 && !warp_wait(SPLASH_BAR(pv_done, s & 1), ((s - 2) >> 1) & 1, ctx, kSiteSmxPv, s)) { alive = false; break; }
         }
         const float m_scaled = (m_run == -INFINITY) ? 0.f : m_run * kLog2e;
         const float2 scale2 = make_float2(kLog2e, kLog2e), shift2 = make_float2(-m_scaled, -m_scaled);
@@ -487,7 +593,7 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
               if (j & 1) sum_b = add2(sum_b, pr); else sum_a = add2(sum_a, pr);
               pk[j] = pack2<BF16>(pr.x, pr.y);
             }
-            tmem_st16(s_tmem + c * 16, pk);
+            tmem_st16(p_tmem + c * 16, pk);
           }
         };
         if (kEmuPairs > 0 && !partial && !a.has_seg) exp_row(std::integral_constant<int, kEmuPairs>{});
@@ -498,7 +604,7 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         // tiles the s_ready wait above already certifies that (the tensor core runs
         // its instructions in issue order); with one tile it is signalled explicitly.
         if constexpr (NT == 1) {
-          if (s > 0 && !warp_wait(SPLASH_BAR(pv_done, 0), (s - 1) & 1, ctx, kSiteSmxPv, s)) { alive = false; break; }
+          if (s > 0 && !warp_wait(SPLASH_BAR(pv_done, (s - 1) & 1), ((s - 1) >> 1) & 1, ctx, kSiteSmxPv, s)) { alive = false; break; }
         }
         if (s > 0 && __any_sync(0xffffffffu, moved)) {
           tc_fence_after();
@@ -515,20 +621,41 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(SPLASH_BAR(p_ready, buf));
-        if (++slot == stages) { slot = 0; phase ^= 1; }
+#pragma unroll
+        for (int i = 0; i < AW; ++i)
+          if (++slot == stages) { slot = 0; phase ^= 1; }
       }
 
       // ---- epilogue: O / l, cast, stage in shared memory, TMA store ---------------
       if (alive) {
         if constexpr (NT == 2) alive = warp_wait(SPLASH_BAR(o_done, 0), 0, ctx, kSiteSmxDone, n);
-        else alive = warp_wait(SPLASH_BAR(pv_done, 0), (n - 1) & 1, ctx, kSiteSmxDone, n);
+        else alive = warp_wait(SPLASH_BAR(pv_done, (n - 1) & 1), ((n - 1) >> 1) & 1, ctx, kSiteSmxDone, n);
+      }
+      float l_tot = l_run;
+      if constexpr (AW == 2) {
+        // Bring both partial sums to the final maximum and add them.  The group that did
+        // not run the last step learns that maximum at the last step's barrier.
+        if (alive && ((n - 1) & 1) != grp)
+          alive = warp_wait(SPLASH_BAR(m_ready, (n - 1) & 1), ((n - 1) >> 1) & 1, ctx, kSiteSmxM, n);
+        if (alive) {
+          const float m_fin = __uint_as_float(lds32(m_sh));
+          if (m_fin != m_run) {
+            l_run = (m_run == -INFINITY) ? 0.f : l_run * ex2_approx((m_run - m_fin) * kLog2e);
+            m_run = m_fin;
+          }
+          sts32(l_sh, __float_as_uint(l_run));
+          mbar_arrive(SPLASH_BAR(fin, 0));
+          alive = warp_wait(SPLASH_BAR(fin, 0), 0, ctx, kSiteSmxFin, n);
+        }
+        if (alive) l_tot = l_run + __uint_as_float(lds32(share_u32 + (1 + (grp ^ 1)) * kTile * 4 + row * 4));
       }
       if (alive) {
         tc_fence_after();
-        const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
+        const float inv_l = l_tot > 0.f ? 1.f / l_tot : 0.f;
         const uint32_t stage = L::kOStageInQ ? (q_u32 + t * (kTile * D * 2)) : v_u32;
 #pragma unroll
-        for (int c = 0; c < DV / 32; ++c) {
+        for (int cc = 0; cc < kEpiCols / 32; ++cc) {
+          const int c = epi_col0 / 32 + cc;
           uint32_t o[32];
           tmem_ld32(o_tmem + c * 32, o);
           tmem_wait_ld();
@@ -543,12 +670,12 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             sts128(box + swz128(row, (c & 1) * 4 + g), w);
           }
         }
-        if (a.lse_out)
+        if (a.lse_out && epi_col0 == 0)
           a.lse_out[static_cast<size_t>(q_row0) + t * kTile + row] =
-              l_run > 0.f ? m_run + lg2_approx(l_run) * kLn2 : a.mask_value;
+              l_tot > 0.f ? m_run + lg2_approx(l_tot) * kLn2 : a.mask_value;
         fence_proxy_async_smem();
         mbar_arrive(SPLASH_BAR(epi, t));
-        if (row == 0) {
+        if (row == 0 && epi_col0 == 0) {
           if (mbar_wait(SPLASH_BAR(epi, t), 0, ctx, kSiteSmxEpi, n)) {
 #pragma unroll
             for (int c = 0; c < DV / 64; ++c)

@@ -3,14 +3,16 @@
 // the kernel for a given (head_dim, head_dim_v, block_kv, tiles) combination.
 #pragma once
 
+#include <cstdlib>
+
 #include "fwd_kernel.cuh"
 #include "host_common.cuh"
 
 namespace splash {
 
-template <int D, int DV, int BKV, int NT, bool BF16>
+template <int D, int DV, int BKV, int NT, int AW, bool BF16>
 int launch_fwd_typed(const SplashParams& p, cudaStream_t stream) {
-  using L = FwdLayout<D, DV, BKV, NT>;
+  using L = FwdLayout<D, DV, BKV, NT, AW>;
   const bool dense = p.partial_blocks != nullptr;
   const bool seg = p.seg_q != nullptr;
   const size_t smem = L::smem_bytes(p.num_stages, dense, seg);
@@ -66,7 +68,7 @@ int launch_fwd_typed(const SplashParams& p, cudaStream_t stream) {
   a.mask_value = p.mask_value;
   a.soft_cap = p.soft_cap;
 
-  auto kernel = splash_fwd_kernel<D, DV, BKV, NT, BF16>;
+  auto kernel = splash_fwd_kernel<D, DV, BKV, NT, AW, BF16>;
   if ((rc = opt_in_smem(kernel, smem))) return rc;
   const unsigned grid = static_cast<unsigned>(a.q_blocks) * p.heads * p.batch;
   kernel<<<grid, L::kThreads, smem, stream>>>(tm_q, tm_k, tm_v, tm_o, tm_mask, a);
@@ -74,10 +76,29 @@ int launch_fwd_typed(const SplashParams& p, cudaStream_t stream) {
   return SPLASH_OK;
 }
 
+// Softmax warpgroups that alternate over the KV steps of a one-tile kernel;
+// SPLASH_FWD_AW=1|2 overrides the default (experiments).
+inline int fwd_alternating_groups() {
+  static const int forced = [] {
+    const char* e = getenv("SPLASH_FWD_AW");
+    return e ? atoi(e) : 0;
+  }();
+  return (forced == 1 || forced == 2) ? forced : 2;
+}
+
 template <int D, int DV, int BKV, int NT>
 int launch_fwd(const SplashParams& p, cudaStream_t stream) {
-  if (p.dtype == SPLASH_DTYPE_BF16) return launch_fwd_typed<D, DV, BKV, NT, true>(p, stream);
-  return launch_fwd_typed<D, DV, BKV, NT, false>(p, stream);
+  const bool bf16 = p.dtype == SPLASH_DTYPE_BF16;
+  // Two alternating groups with 128-column blocks; with 64-column blocks one group
+  // keeps the kernel small enough for two CTAs per SM, which serves that tiling better.
+  if constexpr (NT == 1 && BKV == 128 && 3 * BKV + DV <= 512) {
+    if (fwd_alternating_groups() == 2) {
+      if (bf16) return launch_fwd_typed<D, DV, BKV, NT, 2, true>(p, stream);
+      return launch_fwd_typed<D, DV, BKV, NT, 2, false>(p, stream);
+    }
+  }
+  if (bf16) return launch_fwd_typed<D, DV, BKV, NT, 1, true>(p, stream);
+  return launch_fwd_typed<D, DV, BKV, NT, 1, false>(p, stream);
 }
 
 }  // namespace splash

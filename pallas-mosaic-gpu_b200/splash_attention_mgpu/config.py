@@ -26,9 +26,9 @@ TMEM_COLS = 512
 # and the 1 KiB alignment of swizzled tiles.
 SMEM_BYTES = 227 * 1024 - 4096
 
-# The two-tile forward is chosen automatically for head_dim 128 when its
-# 256-row schedule visits at most this much more KV-block work.
-AUTO_PINGPONG_MAX_EXTRA_WORK = 1.10
+# At head_dim 128 the automatic forward tiling takes 128-wide KV blocks when a
+# 128-row tile visits at least this many of them on average, 64-wide otherwise.
+AUTO_WIDE_BLOCK_MIN_STEPS = 24
 
 
 class SegmentIds(NamedTuple):

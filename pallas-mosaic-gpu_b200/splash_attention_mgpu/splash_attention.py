@@ -34,7 +34,7 @@ from . import _ffi
 from . import config as cfg
 from . import mask_info as mask_info_lib
 from . import splash_attention_mask as mask_lib
-from .config import (AUTO_PINGPONG_MAX_EXTRA_WORK, DEFAULT_MASK_VALUE,
+from .config import (DEFAULT_MASK_VALUE,
                      BlockSizes, SegmentIds, auto_forward_tiles)
 
 _TORCH_DTYPES = {torch.bfloat16: _ffi.DTYPE_BF16, torch.float16: _ffi.DTYPE_F16}
@@ -186,36 +186,47 @@ class SplashAttentionKernel:
     return (float(self.fwd_info(256, 128).num_steps.sum()) * 256
             / max(1.0, float(self.fwd_info(128, 128).num_steps.sum()) * 128))
 
-  def choose_block_q(self, head_dim: int, head_dim_v: int, *,
-                     itemsize: int = 2, has_segments: bool = False,
-                     save_residuals: bool = True) -> int:
+  def _auto_forward_tiling(self, head_dim: int, head_dim_v: int, *,
+                           itemsize: int = 2, has_segments: bool = False,
+                           save_residuals: bool = True) -> tuple[int, int, int]:
+    """(block_q, block_kv, num_stages) when the caller left block_q open.
+
+    At head_dim 128 the one-tile kernel serves every mask measured on B200 at
+    least as well as the two-tile one, in one of two shapes: 64-wide KV blocks
+    with a two-stage ring, which leaves room for two CTAs per SM and suits
+    short rows (local windows, short sequences), and 128-wide blocks with two
+    softmax warpgroups alternating over the KV steps for long rows.  The
+    two-tile kernel (block_q=256) runs when asked for.
+    """
+    if head_dim != head_dim_v or head_dim != 128:
+      bkv, stages = auto_forward_tiles(head_dim, 128)
+      return 128, bkv, stages
+    info = self.fwd_info(128, 128)
+    dense = info.partial_mask_blocks is not None
+    mean_steps = float(info.num_steps.sum()) / max(1, info.num_steps.size)
+    wide = dict(head_dim=head_dim, head_dim_v=head_dim_v, block_kv=128, num_stages=2,
+                itemsize=itemsize, has_dense_mask=dense, has_segments=has_segments,
+                save_residuals=save_residuals)
+    wide_fits = cfg.fwd128_smem_bytes(**wide) <= cfg.SMEM_BYTES
+    if (dense or mean_steps >= cfg.AUTO_WIDE_BLOCK_MIN_STEPS) and wide_fits:
+      return 128, 128, 2
+    return 128, 64, 2
+
+  def choose_block_q(self, head_dim: int, head_dim_v: int, **kw) -> int:
     bs = self.requested_block_sizes
     if bs.block_q is not None:
       return bs.block_q
-    extra = self.pingpong_extra_work
-    if head_dim != head_dim_v or head_dim != 128 or extra is None:
-      return 128
-    if extra > AUTO_PINGPONG_MAX_EXTRA_WORK:
-      return 128
-    bkv, stages = self._tiles(head_dim, 256)
-    if self.mask.shape[-1] % bkv:
-      return 128
-    fits = cfg.pingpong_fits(
-        head_dim=head_dim, block_kv=bkv, num_stages=stages, itemsize=itemsize,
-        has_dense_mask=self.fwd_info(256, bkv).partial_mask_blocks is not None,
-        has_segments=has_segments, save_residuals=save_residuals)
-    return 256 if fits else 128
-
-  def _tiles(self, head_dim: int, block_q: int) -> tuple[int, int]:
-    bs = self.requested_block_sizes
-    auto_kv, auto_stages = auto_forward_tiles(head_dim, block_q)
-    return (bs.block_kv or auto_kv, bs.num_stages or auto_stages)
+    return self._auto_forward_tiling(head_dim, head_dim_v, **kw)[0]
 
   def resolved_block_sizes(self, head_dim: int, head_dim_v: int, **kw) -> BlockSizes:
-    bq = self.choose_block_q(head_dim, head_dim_v, **kw)
-    bkv, stages = self._tiles(head_dim, bq)
-    return dataclasses.replace(self.requested_block_sizes, block_q=bq,
-                               block_kv=bkv, num_stages=stages)
+    bs = self.requested_block_sizes
+    if bs.block_q is None:
+      bq, bkv, stages = self._auto_forward_tiling(head_dim, head_dim_v, **kw)
+    else:
+      bq = bs.block_q
+      bkv, stages = auto_forward_tiles(head_dim, bq)
+    return dataclasses.replace(bs, block_q=bq, block_kv=bs.block_kv or bkv,
+                               num_stages=bs.num_stages or stages)
 
   @property
   def block_sizes(self) -> BlockSizes:

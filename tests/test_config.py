@@ -22,34 +22,45 @@ def test_rejects_invalid_block_sizes():
     sa.BlockSizes(num_stages_bwd=0)
 
 
-def test_auto_block_q_selection():
+def test_auto_forward_tiling_by_row_length():
   s = 4096
-  pick = lambda m, d: sa.make_splash_mha(m).choose_block_q(d, d)
-  assert pick(sa.FullMask((s, s)), 128) == 256
-  assert pick(sa.CausalMask((s, s)), 128) == 256
-  assert pick(sa.ChunkedCausalMask((s, s), 2048), 128) == 256
-  assert pick(sa.LocalMask((s, s), (1024, 0), 0), 128) == 128  # extra work
-  assert pick(sa.FullMask((s, s)), 64) == 128
-  assert pick(sa.FullMask((384, 384)), 128) == 128  # not a multiple of 256
-  assert sa.make_splash_mha(sa.FullMask((s, s)), block_sizes=sa.BlockSizes(block_q=128)
-                            ).choose_block_q(128, 128) == 128
+  tiles = lambda m, d: (lambda bs: (bs.block_q, bs.block_kv, bs.num_stages))(
+      sa.make_splash_mha(m).resolved_block_sizes(d, d))
+  # Long rows: 128-wide blocks, two alternating softmax warpgroups.
+  assert tiles(sa.FullMask((s, s)), 128) == (128, 128, 2)
+  assert tiles(sa.CausalMask((8192, 8192)), 128) == (128, 128, 2)
+  # Short rows: 64-wide blocks and a two-stage ring (two CTAs per SM).
+  assert tiles(sa.CausalMask((2048, 2048)), 128) == (128, 64, 2)
+  assert tiles(sa.LocalMask((s, s), (1024, 0), 0), 128) == (128, 64, 2)
+  assert tiles(sa.ChunkedCausalMask((s, s), 1024), 128) == (128, 64, 2)
+  # Other head dims keep the one-tile defaults.
+  assert tiles(sa.FullMask((s, s)), 64) == (128, 64, 3)
+  assert tiles(sa.FullMask((s, s)), 256) == (128, 128, 2)
+  # The two-tile kernel runs when asked for; open fields are filled in around it.
+  k = sa.make_splash_mha(sa.FullMask((s, s)), block_sizes=sa.BlockSizes(block_q=256))
+  assert k.choose_block_q(128, 128) == 256
+  bs = k.resolved_block_sizes(128, 128)
+  assert (bs.block_q, bs.block_kv, bs.num_stages) == (256, 128, 2)
+  k = sa.make_splash_mha(sa.FullMask((s, s)), block_sizes=sa.BlockSizes(block_kv=64))
+  assert k.resolved_block_sizes(128, 128).block_kv == 64
 
 
-def test_auto_block_q_respects_smem():
+def test_auto_forward_tiling_with_dense_masks():
+  # Streamed mask blocks take the 128-wide tiling: with 64-wide blocks they would
+  # push the kernel past the shared memory that lets two CTAs share an SM.
   dense = np.tril(np.ones((2048, 2048), bool))
-  assert sa.make_splash_mha(sa.NumpyMask(dense)).choose_block_q(128, 128) == 128
-  assert sa.make_splash_mha(sa.NumpyMask(dense), block_sizes=sa.BlockSizes(block_kv=64)
-                            ).choose_block_q(128, 128) == 256
+  bs = sa.make_splash_mha(sa.NumpyMask(dense)).resolved_block_sizes(128, 128)
+  assert (bs.block_q, bs.block_kv, bs.num_stages) == (128, 128, 2)
 
 
 def test_resolved_tiles_of_the_benchmark_configs():
   k = sa.make_splash_mha(sa.CausalMask((8192, 8192)))
   bs = k.resolved_block_sizes(128, 128)
-  assert (bs.block_q, bs.block_kv, bs.num_stages) == (256, 128, 2)
+  assert (bs.block_q, bs.block_kv, bs.num_stages) == (128, 128, 2)
   assert abs(k.pingpong_extra_work - 1056 * 256 / (2080 * 128)) < 1e-9
   k = sa.make_splash_mha(sa.LocalMask((16384, 16384), (1024, 0), 0))
   bs = k.resolved_block_sizes(128, 128)
-  assert (bs.block_q, bs.block_kv, bs.num_stages) == (128, 128, 2)
+  assert (bs.block_q, bs.block_kv, bs.num_stages) == (128, 64, 2)
   k = sa.make_splash_mha(sa.FullMask((8192, 8192)))
   bs = k.resolved_block_sizes(64, 64, has_segments=True)
   assert (bs.block_q, bs.block_kv, bs.num_stages) == (128, 64, 3)

@@ -69,12 +69,14 @@ def test_causal_b2_h16_s8192_d128_forward_backward():
   k, v, do = _rand((2, 16, s, d), dtype, 1), _rand((2, 16, s, d), dtype, 2), _rand((2, 16, s, d), dtype, 3)
   rows = np.sort(np.random.default_rng(0).choice(s, 192, replace=False))
   dense_rows = lambda h, r: (np.arange(s)[None, :] <= r[:, None])
-  for bq in (128, 256):  # the 128-row kernel and the two-tile ping-pong kernel
+  # The two-tile ping-pong kernel, then the one-tile kernel (the automatic choice here).
+  for bq in (256, 128):
     kernel = sa.make_splash_mha(sa.CausalMask((s, s)), block_sizes=sa.BlockSizes(block_q=bq))
     out, (lse,) = kernel(q, k, v, save_residuals=True)
     sa.check_device_status()
     _check_rows(dense_rows, q, k, v, out, lse, rows, heads=[0, 7, 15], dtype=dtype, b=1)
   kernel = sa.make_splash_mha(sa.CausalMask((s, s)))
+  assert kernel.resolved_block_sizes(d, d).block_q == 128
   out2, dq, dk, dv = _grads(kernel, q, k, v, do)
   assert torch.equal(out2, out)
   _check_rows(dense_rows, q, k, v, out, lse, rows, heads=[3], dtype=dtype, b=0, dq=dq, d_out=do)
@@ -91,7 +93,8 @@ def test_local_window_gqa_softcap_s16384_forward_backward():
   k, v, do = _rand((1, 8, s, d), dtype, 1), _rand((1, 8, s, d), dtype, 2), _rand((1, 32, s, d), dtype, 3)
   mask = sa.LocalMask((s, s), (1024, 0), 0)
   kernel = sa.make_splash_mha(mask, attn_logits_soft_cap=cap)
-  assert kernel.resolved_block_sizes(d, d).block_q == 128
+  bs = kernel.resolved_block_sizes(d, d)
+  assert (bs.block_q, bs.block_kv, bs.num_stages) == (128, 64, 2)
   out, (lse,) = kernel(q, k, v, save_residuals=True)
   sa.check_device_status()
   rows = np.sort(np.random.default_rng(1).choice(s, 192, replace=False))

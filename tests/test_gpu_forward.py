@@ -112,19 +112,53 @@ def test_gpu_pingpong(kwargs):
   _check(kwargs.pop("mask_name"), **kwargs)
 
 
-def test_auto_tiles_pick_the_pingpong_kernel_at_head_dim_128():
+def test_auto_tiles_at_head_dim_128():
   kernel = sa.make_splash_mha(sa.CausalMask((2048, 2048)))
-  assert kernel.resolved_block_sizes(128, 128).block_q == 256
+  bs = kernel.resolved_block_sizes(128, 128)
+  assert (bs.block_q, bs.block_kv, bs.num_stages) == (128, 64, 2)
   _check("causal", d=128, h=2)
 
 
-@pytest.mark.parametrize("bq", [128, 256])
-def test_gpu_empty_rows_are_zero(bq):
+# 128-wide KV blocks in the one-tile kernel: two softmax warpgroups alternate over the
+# KV steps and pass the running row maximum to one another.
+WIDE = sa.BlockSizes(block_q=128, block_kv=128)
+WIDE_CASES = [
+    dict(mask_name="full", d=128),
+    dict(mask_name="causal", d=128),
+    dict(mask_name="local", d=128),
+    dict(mask_name="chunked", d=128),
+    dict(mask_name="dense", d=128),
+    dict(mask_name="causal", d=128, s=128),   # one step: the second group never runs one
+    dict(mask_name="causal", d=128, s=256),
+    dict(mask_name="full", d=128, s=384),     # odd number of steps
+    dict(mask_name="causal", d=128, segs=True),
+    dict(mask_name="dense", d=128, segs=True),
+    dict(mask_name="causal", d=128, cap=5.0),
+    dict(mask_name="causal", d=128, h=4, kvh=2),
+    dict(mask_name="full", d=128, mqa=True, b=2),
+    dict(mask_name="causal", d=128, multi_head_mask=True, h=3),
+    dict(mask_name="causal", d=128, dtype=torch.float16),
+    dict(mask_name="causal", d=64),
+    dict(mask_name="dense", d=64, segs=True),
+    dict(mask_name="causal", d=64, dv=128),
+    dict(mask_name="causal", d=128, dv=64),
+]
+
+
+@pytest.mark.parametrize("kwargs", WIDE_CASES, ids=_id)
+def test_gpu_alternating_warpgroups(kwargs):
+  kwargs = dict(kwargs)
+  kwargs.setdefault("block_sizes", WIDE)
+  _check(kwargs.pop("mask_name"), **kwargs)
+
+
+@pytest.mark.parametrize("bq,bkv", [(128, None), (128, 128), (256, None)])
+def test_gpu_empty_rows_are_zero(bq, bkv):
   # The first q block sees nothing: its output is zero and lse = mask_value.
   s = 512
   dense = np.zeros((s, s), bool)
   dense[256:, :] = True
-  kernel = sa.make_splash_mha(sa.NumpyMask(dense), block_sizes=sa.BlockSizes(block_q=bq))
+  kernel = sa.make_splash_mha(sa.NumpyMask(dense), block_sizes=sa.BlockSizes(block_q=bq, block_kv=bkv))
   q, k, v = inputs(None, 1, 1, s, 64, 64, torch.bfloat16, False, device="cuda:0")
   out, (lse,) = kernel(q, k, v, save_residuals=True)
   sa.check_device_status()
@@ -134,11 +168,13 @@ def test_gpu_empty_rows_are_zero(bq):
   np.testing.assert_allclose(out[:, 256:].float().cpu().numpy(), ref[:, 256:], atol=2e-2, rtol=2e-2)
 
 
-@pytest.mark.parametrize("growth", [0.0, 0.05, 40.0])
-@pytest.mark.parametrize("bq", [128, 256])
-def test_gpu_lazy_rescaling(growth, bq):
+@pytest.mark.parametrize("growth", [0.0, 0.05, 40.0, -40.0])
+@pytest.mark.parametrize("bq,bkv", [(128, None), (128, 128), (256, None)])
+def test_gpu_lazy_rescaling(growth, bq, bkv):
+  # Logits that drift up (or down) along the keys: the running maximum moves at every
+  # step, at some steps only, or never, and O is rescaled accordingly.
   s, d = 1024, 64
-  kernel = sa.make_splash_mha(sa.CausalMask((s, s)), block_sizes=sa.BlockSizes(block_q=bq))
+  kernel = sa.make_splash_mha(sa.CausalMask((s, s)), block_sizes=sa.BlockSizes(block_q=bq, block_kv=bkv))
   q, k, v = inputs(None, 2, 2, s, d, d, torch.bfloat16, False)
   pos = torch.arange(s, dtype=torch.float32)[None, :, None] / s
   k = (k.float() * 0.3 + growth * pos).to(torch.bfloat16).cuda()
@@ -155,7 +191,7 @@ def test_rejects_oversized_configs():
   q, k, v = inputs(None, 1, 1, 512, 256, 256, torch.bfloat16, False, device="cuda:0")
   with pytest.raises(ValueError, match="TMEM budget"):
     kernel(q, k, v)
-  kernel = sa.make_splash_mha(sa.CausalMask((512, 512)), block_sizes=sa.BlockSizes(num_stages=3))
+  kernel = sa.make_splash_mha(sa.CausalMask((512, 512)), block_sizes=sa.BlockSizes(block_kv=128, num_stages=4))
   q, k, v = inputs(None, 1, 1, 512, 128, 128, torch.bfloat16, False, device="cuda:0")
   with pytest.raises(ValueError, match="Shared memory budget"):
     kernel(q, k, v)
