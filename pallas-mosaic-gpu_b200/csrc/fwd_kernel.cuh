@@ -273,8 +273,10 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       if (elect_one()) prefetch_tensormap(&tm_v);
       int slot = 0;
       uint32_t phase = 0;
+      int j_next = a.block_list[sched_off];
       for (int s = 0; s < n; ++s) {
-        const int kv_row = kv_row0 + a.block_list[sched_off + s] * BKV;
+        const int kv_row = kv_row0 + j_next * BKV;
+        if (s + 1 < n) j_next = a.block_list[sched_off + s + 1];
         if (s >= stages && !warp_wait(SPLASH_BAR(v_empty, slot), phase ^ 1, ctx, kSiteTmaVEmpty, s)) break;
         if (elect_one()) {
           mbar_arrive_expect_tx(SPLASH_BAR(v_full, slot), L::kVStage);
