@@ -49,7 +49,8 @@ typedef struct SplashParams {
   const void* v;           /* [batch, kv_heads, kv_len, head_dim_v]             */
   const void* d_out;       /* backward: [batch, heads, q_len, head_dim_v]       */
   const float* lse;        /* backward: [batch, heads, q_len], natural log      */
-  const float* delta;      /* backward: [batch, heads, q_len] = sum(dO * O)     */
+  float* delta;            /* backward: [batch, heads, q_len] = sum(dO * O); written
+                            * by splash_bwd_fused when `out` is set, read otherwise */
   const int32_t* seg_q;    /* [batch, q_len] or NULL                            */
   const int32_t* seg_kv;   /* [batch, kv_len] or NULL                           */
   /* Sparse schedule.  Forward and dQ use the per-q-block ("row") lists; dK/dV
@@ -115,7 +116,11 @@ int splash_bwd_dkv(const SplashParams* p, void* stream);
 /* Fused backward (dQ, dK, dV in one kernel; dQ reduce-added into `dq_acc`, which
  * this call zeroes first and converts into `dq` afterwards).  Replaces
  * `splash_attention_bwd_fused` together with its accumulator zero-fill and
- * transpose/cast passes (reference splash_attention_mgpu/backward_fused.py:492-511). */
+ * transpose/cast passes (reference splash_attention_mgpu/backward_fused.py:492-511).
+ * With `out` null, `delta` must already hold rowsum(dO * O) (splash_bwd_delta); with
+ * `out` set to the forward output, this call fills `delta` itself in the pass that
+ * clears the accumulator (what the reference leaves to XLA,
+ * splash_attention_mgpu/splash_attention.py:289-290). */
 int splash_bwd_fused(const SplashParams* p, void* stream);
 
 /* Bytes of `dq_acc` scratch splash_bwd_fused needs for these shapes. */

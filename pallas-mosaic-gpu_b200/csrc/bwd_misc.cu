@@ -21,76 +21,113 @@ __device__ __forceinline__ float2 unpack2(uint32_t w) {
   }
 }
 
-// One warp per row; each lane handles 16-byte chunks (8 elements).
+// One warp per group of kRows rows; each lane handles 16-byte chunks (8 elements) and
+// keeps the loads of all its rows in flight together.  When `zero` is given, the warp
+// also clears `zero_vec_per_row` float4 per row of it: the fused backward gets its f32
+// dQ accumulator cleared by the pass that already streams O and dO.
+constexpr int kDeltaRows = 4;
+
 template <bool BF16>
 __global__ void __launch_bounds__(256) delta_kernel(const uint4* __restrict__ o, const uint4* __restrict__ d_out,
-                                                    float* __restrict__ delta, long long rows, int chunks_per_row) {
-  const long long row = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+                                                    float* __restrict__ delta, long long rows, int chunks_per_row,
+                                                    float4* __restrict__ zero, int zero_vec_per_row) {
+  const long long row0 = (static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5)) * kDeltaRows;
   const int lane = threadIdx.x & 31;
-  if (row >= rows) return;
-  float acc = 0.f;
-  for (int c = lane; c < chunks_per_row; c += 32) {
-    const uint4 a = o[row * chunks_per_row + c];
-    const uint4 b = d_out[row * chunks_per_row + c];
-    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+  if (row0 >= rows) return;
+  float acc[kDeltaRows];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float2 x = unpack2<BF16>(aw[i]), y = unpack2<BF16>(bw[i]);
-      acc = fmaf(x.x, y.x, acc);
-      acc = fmaf(x.y, y.y, acc);
+  for (int r = 0; r < kDeltaRows; ++r) acc[r] = 0.f;
+  for (int c = lane; c < chunks_per_row; c += 32) {
+    uint4 a[kDeltaRows], b[kDeltaRows];
+#pragma unroll
+    for (int r = 0; r < kDeltaRows; ++r) {
+      const bool live = row0 + r < rows;
+      a[r] = live ? o[(row0 + r) * chunks_per_row + c] : make_uint4(0, 0, 0, 0);
+      b[r] = live ? d_out[(row0 + r) * chunks_per_row + c] : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int r = 0; r < kDeltaRows; ++r) {
+      const uint32_t aw[4] = {a[r].x, a[r].y, a[r].z, a[r].w}, bw[4] = {b[r].x, b[r].y, b[r].z, b[r].w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 x = unpack2<BF16>(aw[i]), y = unpack2<BF16>(bw[i]);
+        acc[r] = fmaf(x.x, y.x, acc[r]);
+        acc[r] = fmaf(x.y, y.y, acc[r]);
+      }
     }
   }
+  if (zero) {
+    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-  for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
-  if (lane == 0) delta[row] = acc;
+    for (int r = 0; r < kDeltaRows; ++r)
+      if (row0 + r < rows)
+        for (int c = lane; c < zero_vec_per_row; c += 32) zero[(row0 + r) * zero_vec_per_row + c] = z;
+  }
+#pragma unroll
+  for (int r = 0; r < kDeltaRows; ++r) {
+    float v = acc[r];
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) v += __shfl_xor_sync(0xffffffffu, v, s);
+    if (lane == 0 && row0 + r < rows) delta[row0 + r] = v;
+  }
 }
 
 int launch_delta(const void* o, const void* d_out, float* delta, long long rows, int head_dim_v, int dtype,
-                 cudaStream_t stream) {
+                 cudaStream_t stream, float* zero, int zero_floats_per_row) {
   if (!o || !d_out || !delta || rows <= 0 || head_dim_v % 8) return fail(SPLASH_INVALID_ARGUMENT, "bad delta arguments");
-  const unsigned grid = static_cast<unsigned>((rows + 7) / 8);
+  if (zero && zero_floats_per_row % 4) return fail(SPLASH_INVALID_ARGUMENT, "bad delta arguments");
+  const unsigned grid = static_cast<unsigned>((rows + 8 * kDeltaRows - 1) / (8 * kDeltaRows));
   if (dtype == SPLASH_DTYPE_BF16)
     delta_kernel<true><<<grid, 256, 0, stream>>>(static_cast<const uint4*>(o), static_cast<const uint4*>(d_out), delta,
-                                                  rows, head_dim_v / 8);
+                                                  rows, head_dim_v / 8, reinterpret_cast<float4*>(zero),
+                                                  zero_floats_per_row / 4);
   else
     delta_kernel<false><<<grid, 256, 0, stream>>>(static_cast<const uint4*>(o), static_cast<const uint4*>(d_out), delta,
-                                                   rows, head_dim_v / 8);
+                                                   rows, head_dim_v / 8, reinterpret_cast<float4*>(zero),
+                                                   zero_floats_per_row / 4);
   SPLASH_CUDA_CHECK(cudaGetLastError());
   return SPLASH_OK;
 }
 
-// acc: [bh, d, q] f32  ->  dq: [bh, q, d] 16-bit.  Tiles of 32 (d) x 64 (q).
+// acc: [bh, d, q] f32  ->  dq: [bh, q, d] 16-bit, in tiles of 64 (d) x 64 (q).  Reads are
+// 256-byte runs along q; each warp store covers 128 contiguous bytes along d.
 template <bool BF16>
 __global__ void __launch_bounds__(256) dq_transpose_cast_kernel(const float* __restrict__ acc, uint16_t* __restrict__ dq,
                                                                 int head_dim, int q_len) {
-  __shared__ float tile[32][65];
+  __shared__ float tile[64][65];
   const long long bh = blockIdx.z;
-  const int d0 = blockIdx.y * 32, q0 = blockIdx.x * 64;
+  const int d0 = blockIdx.y * 64, q0 = blockIdx.x * 64;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const float* src = acc + (bh * head_dim + d0) * static_cast<long long>(q_len) + q0;
-  for (int i = threadIdx.x; i < 32 * 64; i += 256) {
-    const int d = i / 64, q = i % 64;
-    tile[d][q] = src[static_cast<long long>(d) * q_len + q];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int d = warp * 8 + i;
+    const float2 v = *reinterpret_cast<const float2*>(src + static_cast<long long>(d) * q_len + 2 * lane);
+    tile[d][2 * lane] = v.x;
+    tile[d][2 * lane + 1] = v.y;
   }
   __syncthreads();
   uint16_t* dst = dq + (bh * q_len + q0) * static_cast<long long>(head_dim) + d0;
-  for (int i = threadIdx.x; i < 64 * 16; i += 256) {
-    const int q = i / 16, dp = (i % 16) * 2;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int q = warp * 8 + i;
+    const float lo = tile[2 * lane][q], hi = tile[2 * lane + 1][q];
     uint32_t w;
     if constexpr (BF16) {
-      const __nv_bfloat162 v = __floats2bfloat162_rn(tile[dp][q], tile[dp + 1][q]);
+      const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
       w = *reinterpret_cast<const uint32_t*>(&v);
     } else {
-      const __half2 v = __floats2half2_rn(tile[dp][q], tile[dp + 1][q]);
+      const __half2 v = __floats2half2_rn(lo, hi);
       w = *reinterpret_cast<const uint32_t*>(&v);
     }
-    *reinterpret_cast<uint32_t*>(dst + static_cast<long long>(q) * head_dim + dp) = w;
+    *reinterpret_cast<uint32_t*>(dst + static_cast<long long>(q) * head_dim + 2 * lane) = w;
   }
 }
 
 int launch_dq_transpose_cast(const float* acc, void* dq, long long batch_heads, int head_dim, int q_len, int dtype,
                              cudaStream_t stream) {
-  if (!acc || !dq || head_dim % 32 || q_len % 64) return fail(SPLASH_INVALID_ARGUMENT, "bad dq cast arguments");
-  dim3 grid(q_len / 64, head_dim / 32, static_cast<unsigned>(batch_heads));
+  if (!acc || !dq || head_dim % 64 || q_len % 64) return fail(SPLASH_INVALID_ARGUMENT, "bad dq cast arguments");
+  dim3 grid(q_len / 64, head_dim / 64, static_cast<unsigned>(batch_heads));
   if (dtype == SPLASH_DTYPE_BF16)
     dq_transpose_cast_kernel<true><<<grid, 256, 0, stream>>>(acc, static_cast<uint16_t*>(dq), head_dim, q_len);
   else

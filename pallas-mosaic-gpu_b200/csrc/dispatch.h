@@ -25,8 +25,9 @@ template <int D, int DV, int BC>
 size_t bwd_row_smem(const SplashParams& p);
 
 // delta = rowsum(dO * O); dq = cast(transpose(dq_acc)).
+// When `zero` is non-null the same pass also clears zero_floats_per_row floats per row of it.
 int launch_delta(const void* o, const void* d_out, float* delta, long long rows, int head_dim_v, int dtype,
-                 cudaStream_t stream);
+                 cudaStream_t stream, float* zero = nullptr, int zero_floats_per_row = 0);
 int launch_dq_transpose_cast(const float* acc, void* dq, long long batch_heads, int head_dim, int q_len, int dtype,
                              cudaStream_t stream);
 

@@ -470,12 +470,14 @@ def _backward(kernel: SplashAttentionKernel, bs: BlockSizes, q, k, v,
   dq = torch.empty_like(q)
   dk = torch.empty_like(k)
   dv = torch.empty_like(v)
+  fused = _use_fused_backward(q, v, bs, has_dense, has_segments)
   with torch.cuda.device(q.device):
     stream = torch.cuda.current_stream(q.device).cuda_stream
-    _ffi.check(lib.splash_bwd_delta(out.data_ptr(), d_out.data_ptr(),
-                                    delta.data_ptr(), batch * heads * q_len,
-                                    head_dim_v, _TORCH_DTYPES[q.dtype], stream),
-               "splash attention delta")
+    if not fused:
+      _ffi.check(lib.splash_bwd_delta(out.data_ptr(), d_out.data_ptr(),
+                                      delta.data_ptr(), batch * heads * q_len,
+                                      head_dim_v, _TORCH_DTYPES[q.dtype], stream),
+                 "splash attention delta")
 
     def params(sched):
       p = _base_params(kernel, q, k, v, segment_ids, sched)
@@ -485,8 +487,9 @@ def _backward(kernel: SplashAttentionKernel, bs: BlockSizes, q, k, v,
       p.num_stages = bs.num_stages_bwd
       return p
 
-    if _use_fused_backward(q, v, bs, has_dense, has_segments):
+    if fused:
       p = params(cols)
+      p.out = out.data_ptr()  # delta is computed in the pass that clears the accumulator
       nbytes = lib.splash_bwd_fused_workspace_bytes(ctypes.byref(p))
       acc = torch.empty(max(int(nbytes), 4) // 4, dtype=torch.float32,
                         device=q.device)
