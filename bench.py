@@ -5,8 +5,8 @@
 One "step" is one forward + one backward pass of splash attention over one batch of
 seeded synthetic inputs.  The default workload is the one the headline metric is
 quoted on: CausalMask MHA, batch 2, 16 heads, seq 8192, head_dim 128, bf16 with f32
-accumulation, q pre-scaled by 1/sqrt(128), automatic tiles (256-row ping-pong
-forward, fused backward).  Useful FLOPs follow the reference's accounting
+accumulation, q pre-scaled by 1/sqrt(128), automatic tiles (128-row forward with
+128-wide KV blocks and two alternating softmax warpgroups, fused backward).  Useful FLOPs follow the reference's accounting
 (tools/bench.py:86-102): 4 * visible 128x128 blocks * 128 * 128 * head_dim per
 forward, 3.5x that for forward + backward.
 
@@ -19,6 +19,10 @@ Multi-GPU: one process per GPU (torchrun), every rank runs its own copy of the
 workload -- the (batch x kv-head) units are independent, so there is no collective
 on the data path ("weak" scaling); NCCL carries only the barrier and the max of the
 per-rank times.
+
+`sdpa` (rank 0, one GPU, full and causal workloads) is torch's scaled_dot_product_attention
+restricted to its cuDNN backend on the same GPU and inputs: a library comparator, not
+part of the measured path; --no-sdpa skips it.
 
 --impl reference times the CPU restatement of the reference's dense f32 attention
 (oracle/dense_attention.py) on the host cores over a bounded sample of the same
@@ -309,22 +313,34 @@ def run_ours(args):
     value = world * fb_flops / (ms_per_step * 1e-3) / 1e12
     fwd_tflops = fwd_flops / (fwd_ms * 1e-3) / 1e12
     bwd_tflops = (fb_flops - fwd_flops) / (bwd_ms * 1e-3) / 1e12
-    # Dominant launch group: the backward call (delta pre-pass, accumulator clear, fused
-    # kernel, transpose-cast); its algorithmic work is 2.5x the forward FLOPs.
+    # Dominant launch group: the backward call (delta pass that also clears the dQ
+    # accumulator, fused kernel, transpose-cast); its algorithmic work is 2.5x the forward FLOPs.
     # `traffic`: dram__bytes_read + dram__bytes_write of that kernel from the committed ncu
     # capture of this same workload (profiles/ncu_*_causal_s8192_d128.md), bytes per launch.
     default_wl = workload == DEFAULT_WORKLOAD
     roofline = dict(bound="tensor", achieved=bwd_tflops, peak=peaks["sustained"], unit="TFLOP/s",
-                    frac=bwd_tflops / peaks["sustained"], traffic=630.6e6 if default_wl else None,
+                    frac=bwd_tflops / peaks["sustained"], traffic=630.9e6 if default_wl else None,
                     peak_source=peaks["source"] + " sustained bf16",
-                    kernel="splash_bwd_col_kernel<128,fused> (93% of the backward launch group; timed with its "
-                           "delta pre-pass, accumulator clear and transpose-cast)" if d == 128 else
+                    kernel="splash_bwd_col_kernel<128,fused> (about 95% of the backward launch group; timed with its "
+                           "delta pass, which also clears the dQ accumulator, and the transpose-cast)" if d == 128 else
                            "splash_bwd_row_kernel + splash_bwd_col_kernel (+delta)",
                     frac_of_nominal_2250=bwd_tflops / 2250.0)
     roofline_fwd = dict(bound="tensor", achieved=fwd_tflops, peak=peaks["sustained"], unit="TFLOP/s",
-                        frac=fwd_tflops / peaks["sustained"], traffic=251.2e6 if default_wl else None,
+                        frac=fwd_tflops / peaks["sustained"], traffic=255.0e6 if default_wl else None,
                         kernel=f"splash_fwd_kernel<block_q={bs.block_q},block_kv={bs.block_kv}>",
                         frac_of_nominal_2250=fwd_tflops / 2250.0)
+    sdpa = None
+    if world == 1 and not args.no_sdpa and kind in ("full", "causal") and cap is None:
+      from splash_attention_mgpu import tuning
+      t = tuning.sdpa_baseline(q.detach(), k.detach(), v.detach(), do, causal=kind == "causal", backend="cudnn")
+      if t.fwd_ms is None:
+        sdpa = dict(backend="cudnn", unavailable=t.error)
+      else:
+        sdpa = dict(backend="cudnn", fwd_tflops=fwd_flops / (t.fwd_ms * 1e9),
+                    bwd_tflops=(fb_flops - fwd_flops) / (t.bwd_ms * 1e9) if t.bwd_ms else None,
+                    fwd_bwd_tflops=fb_flops / ((t.fwd_ms + (t.bwd_ms or 0.0)) * 1e9) if t.bwd_ms else None,
+                    fwd_ms=t.fwd_ms, bwd_ms=t.bwd_ms, note="torch SDPA on the same GPU and inputs; a library "
+                    "comparator outside the measured path")
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
       val, sec, threads, n = cpu_sample(workload, 2)
@@ -341,7 +357,7 @@ def run_ours(args):
                     f"= {8 * batch * heads * seq * d * 2 / 2**20:.0f} MiB per step)",
                     per_rank="every rank runs the whole workload"),
         fwd_tflops=world * fwd_tflops, fwd_ms=fwd_ms, bwd_ms=bwd_ms,
-        roofline=roofline, roofline_fwd=roofline_fwd, cpu_baseline=cpu,
+        roofline=roofline, roofline_fwd=roofline_fwd, cpu_baseline=cpu, sdpa=sdpa,
         e2e=dict(value=world * fb_flops / (e2e_ms / args.steps * 1e-3) / 1e12, unit=UNIT,
                  h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h, ms_per_step=e2e_ms / args.steps),
         gpu_launches=launches_per_step * args.steps, clocks=clocks,
@@ -360,6 +376,7 @@ def main():
   p.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
   p.add_argument("--no-cpu-baseline", action="store_true")
   p.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (used when profiling)")
+  p.add_argument("--no-sdpa", action="store_true", help="skip the torch SDPA (cuDNN) comparator")
   args = p.parse_args()
   if args.impl == "reference":
     run_reference(args)
