@@ -13,7 +13,8 @@ forward, 3.5x that for forward + backward.
 Prints ONE JSON line.  `value` is forward+backward useful TFLOP/s summed over all
 ranks with inputs resident in HBM; `e2e` is the same metric through the public API
 with host buffers (pinned host -> device copies of q, k, v, dO and device -> host
-copies of out, dq, dk, dv inside the timed region).
+copies of out, dq, dk, dv of every step inside the timed region, pipelined over a
+copy-in, a compute and a copy-out stream).
 
 Multi-GPU: one process per GPU (torchrun), every rank runs its own copy of the
 workload -- the (batch x kv-head) units are independent, so there is no collective
@@ -276,26 +277,48 @@ def run_ours(args):
   out_h = torch.empty((batch, heads, seq, d), dtype=dtype).pin_memory()
   dq_h, dk_h, dv_h = (torch.empty_like(x).pin_memory() for x in (hq, hk, hv))
 
-  def e2e_step():
-    qd = hq.to(dev, non_blocking=True).requires_grad_(True)
-    kd = hk.to(dev, non_blocking=True).requires_grad_(True)
-    vd = hv.to(dev, non_blocking=True).requires_grad_(True)
-    dod = hdo.to(dev, non_blocking=True)
+  # Three streams, the way a caller that feeds host batches would run it: the inputs of
+  # step i+1 are copied in while step i computes and the results of step i-1 are copied
+  # out (PCIe carries both directions at once).  Two sets of device input buffers; a set
+  # is reused only after the step that read it has finished.
+  copy_in, copy_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+  compute = torch.cuda.current_stream(dev)
+  dev_in = [[torch.empty_like(x, device=dev) for x in (hq, hk, hv, hdo)] for _ in range(2)]
+  in_ready = [torch.cuda.Event() for _ in range(2)]
+  in_free = [torch.cuda.Event() for _ in range(2)]
+  out_done = torch.cuda.Event()
+
+  def e2e_step(i):
+    slot = i % 2
+    with torch.cuda.stream(copy_in):
+      if i >= 2:
+        copy_in.wait_event(in_free[slot])
+      for dst, src in zip(dev_in[slot], (hq, hk, hv, hdo)):
+        dst.copy_(src, non_blocking=True)
+      in_ready[slot].record(copy_in)
+    compute.wait_event(in_ready[slot])
+    qd, kd, vd = (x.detach().requires_grad_(True) for x in dev_in[slot][:3])
     o = kernel(qd, kd, vd)
-    o.backward(dod)
-    out_h.copy_(o.detach(), non_blocking=True)
-    dq_h.copy_(qd.grad, non_blocking=True)
-    dk_h.copy_(kd.grad, non_blocking=True)
-    dv_h.copy_(vd.grad, non_blocking=True)
+    o.backward(dev_in[slot][3])
+    in_free[slot].record(compute)
+    results = (o.detach(), qd.grad, kd.grad, vd.grad)
+    with torch.cuda.stream(copy_out):
+      copy_out.wait_event(in_free[slot])
+      for dst, src in zip((out_h, dq_h, dk_h, dv_h), results):
+        src.record_stream(copy_out)
+        dst.copy_(src, non_blocking=True)
+      out_done.record(copy_out)
 
   e2e_ms = float("nan")
   if not args.no_e2e:
-    e2e_step()
+    for i in range(2):
+      e2e_step(i)
     barrier()
     e_start, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e_start.record()
-    for _ in range(args.steps):
-      e2e_step()
+    for i in range(args.steps):
+      e2e_step(i + 2)
+    compute.wait_event(out_done)  # the last step's results have reached the host
     e_end.record()
     barrier()
     e2e_ms = e_start.elapsed_time(e_end)
