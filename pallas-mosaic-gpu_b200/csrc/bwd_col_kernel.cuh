@@ -112,7 +112,6 @@ struct ColBarriers {
   uint64_t epi[2];
   uint32_t tmem_base;
   uint32_t abort_flag;
-  uint32_t dead;
 };
 
 #define SPLASH_CBAR(field, idx) \
@@ -189,7 +188,6 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const uint32_t segq_u32 = delta_u32 + stages * L::kVecStage;
   const uint32_t bars_u32 = (segq_u32 + (a.has_seg ? stages * L::kVecStage : 0) + 15u) & ~15u;
   const uint32_t abort_u32 = bars_u32 + static_cast<uint32_t>(offsetof(ColBarriers, abort_flag));
-  const uint32_t dead_u32 = bars_u32 + static_cast<uint32_t>(offsetof(ColBarriers, dead));
   const uint32_t tmem_slot_u32 = bars_u32 + static_cast<uint32_t>(offsetof(ColBarriers, tmem_base));
 
   const int warp = uniform_warp_index();
@@ -210,30 +208,24 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   it.init(&a, kj, head0, group);
   const int total = it.total();
 
-  if (threadIdx.x == 0) {
-    sts32(abort_u32, 0);
-    sts32(dead_u32, a.status[0] != 0);
-    mbar_init(SPLASH_CBAR(kv_full, 0), 1);
-    for (int i = 0; i < stages; ++i) {
-      mbar_init(SPLASH_CBAR(full, i), 1);
-      mbar_init(SPLASH_CBAR(empty, i), 1 + kEwWarps);
+  // One warp initialises the barriers, a lane each, while the MMA warp allocates tensor
+  // memory; one CTA barrier later every role starts.  A launch that finds the status
+  // word already set returns without touching data.
+  const bool dead = a.status[0] != 0;
+  if (warp == 0) {
+    constexpr uint32_t kNumBarriers = offsetof(ColBarriers, tmem_base) / 8;
+    for (uint32_t i = lane; i < kNumBarriers; i += 32) {
+      const uint32_t off = 8u * i;
+      uint32_t count = 1;
+      if (off >= offsetof(ColBarriers, empty) && off < offsetof(ColBarriers, s_ready)) count = 1 + kEwWarps;
+      if (off >= offsetof(ColBarriers, p_ready) && off < offsetof(ColBarriers, acc_done)) count = L::kEwThreads;
+      if (off >= offsetof(ColBarriers, dq_free) && off < offsetof(ColBarriers, tmem_base)) count = 128;  // dq_free, wr_a, wr_b, epi
+      mbar_init(bars_u32 + off, count);
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(SPLASH_CBAR(s_ready, i), 1);
-      mbar_init(SPLASH_CBAR(p_ready, i), L::kEwThreads);
-      mbar_init(SPLASH_CBAR(epi, i), 128);
-    }
-    mbar_init(SPLASH_CBAR(acc_done, 0), 1);
-    mbar_init(SPLASH_CBAR(dq_ready, 0), 1);
-    mbar_init(SPLASH_CBAR(dq_free, 0), 128);
-    mbar_init(SPLASH_CBAR(wr_a, 0), 128);
-    mbar_init(SPLASH_CBAR(wr_b, 0), 128);
+    if (lane == 0) sts32(abort_u32, 0);
     fence_mbar_init();
     fence_proxy_async_smem();
-  }
-  __syncthreads();
-  if (lds32(dead_u32)) return;
-  if (warp == kProducerWarp0 + 1) {
+  } else if (warp == kProducerWarp0 + 1) {
     tmem_alloc(tmem_slot_u32, L::kTmemCols);
     tmem_relinquish();
   }
@@ -242,6 +234,13 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   tc_fence_after();
   const uint32_t tmem = lds32(tmem_slot_u32);
   const WaitCtx ctx{abort_u32, a.status};
+  if (dead) {
+    if (warp == kProducerWarp0 + 1) {
+      __syncwarp();
+      tmem_dealloc(tmem, L::kTmemCols);
+    }
+    return;
+  }
   constexpr uint32_t kDescHi = desc_hi(1024);
 
   if (warp >= kProducerWarp0) {
@@ -427,7 +426,7 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           }
         }
       }
-      if (leader) bulk_wait_group<0>();
+      if (leader) bulk_wait_group_read<0>();
     }
   } else {
     // ========================== elementwise warpgroups ===========================
@@ -625,7 +624,7 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             for (int c = 0; c < kCols / 64; ++c)
               tma_store_2d(w == 0 ? &tm_dk : &tm_dv, stage + c * (kRows * 128), c * 64, kv_row0);
             bulk_commit_group();
-            bulk_wait_group<0>();
+            bulk_wait_group_read<0>();
           }
         }
       }

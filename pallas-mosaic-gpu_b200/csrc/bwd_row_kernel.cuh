@@ -377,7 +377,7 @@ splash_bwd_row_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 #pragma unroll
             for (int c = 0; c < D / 64; ++c) tma_store_2d(&tm_dq, q_u32 + c * (kRows * 128), c * 64, q_row0);
             bulk_commit_group();
-            bulk_wait_group<0>();
+            bulk_wait_group_read<0>();
           }
         }
       }

@@ -124,7 +124,6 @@ struct FwdBarriers {
   uint64_t fin;         // alternating warpgroups: partial row sums posted
   uint32_t tmem_base;
   uint32_t abort_flag;
-  uint32_t dead;  // status word was already non-zero at entry
 };
 
 #define SPLASH_BAR(field, idx) \
@@ -151,7 +150,6 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const uint32_t bars_u32 = seg_u32 + (a.has_seg ? stages * L::kSegStage : 0);
   const uint32_t share_u32 = bars_u32 + 1024;  // [row maxima | partial sums of group 0 | of group 1]
   const uint32_t abort_u32 = bars_u32 + static_cast<uint32_t>(offsetof(FwdBarriers, abort_flag));
-  const uint32_t dead_u32 = bars_u32 + static_cast<uint32_t>(offsetof(FwdBarriers, dead));
   const uint32_t tmem_slot_u32 = bars_u32 + static_cast<uint32_t>(offsetof(FwdBarriers, tmem_base));
 
   const int warp = uniform_warp_index();
@@ -170,35 +168,26 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const int q_row0 = (b * a.heads + h) * a.q_len + qi * kBq;   // row in the [B*H*Sq, D] view
 
   // ---- set-up -----------------------------------------------------------------
-  if (threadIdx.x == 0) {
-    sts32(abort_u32, 0);
-    sts32(dead_u32, a.status[0] != 0);
-    mbar_init(SPLASH_BAR(q_full, 0), 1);
-    for (int i = 0; i < stages; ++i) {
-      mbar_init(SPLASH_BAR(k_full, i), 1);
-      mbar_init(SPLASH_BAR(k_empty, i), 1);
-      mbar_init(SPLASH_BAR(v_full, i), 1);
-      mbar_init(SPLASH_BAR(v_empty, i), 1);
-      mbar_init(SPLASH_BAR(aux_full, i), 1);
-      mbar_init(SPLASH_BAR(aux_empty, i), 4 * NT);  // the warps that consume one step
+  // One warp initialises the barriers, a lane each, while the MMA warp allocates tensor
+  // memory; one CTA barrier later every role starts.  A launch that finds the status
+  // word already set (an earlier kernel gave up a wait) returns without touching data.
+  const bool dead = a.status[0] != 0;
+  if (warp == 0) {
+    constexpr uint32_t kNumBarriers = offsetof(FwdBarriers, tmem_base) / 8;
+    for (uint32_t i = lane; i < kNumBarriers; i += 32) {
+      const uint32_t off = 8u * i;
+      uint32_t count = 1;
+      if (off >= offsetof(FwdBarriers, aux_empty) && off < offsetof(FwdBarriers, s_ready)) count = 4 * NT;  // the warps that consume one step
+      if (off >= offsetof(FwdBarriers, p_ready) && off < offsetof(FwdBarriers, pv_done)) count = kTile;
+      if (off >= offsetof(FwdBarriers, epi) && off < offsetof(FwdBarriers, s_free)) count = kTile * AW;
+      if (off >= offsetof(FwdBarriers, s_free) && off < offsetof(FwdBarriers, fin)) count = kTile;  // s_free, m_ready
+      if (off == offsetof(FwdBarriers, fin)) count = kTile * AW;
+      mbar_init(bars_u32 + off, count);
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(SPLASH_BAR(s_ready, i), 1);
-      mbar_init(SPLASH_BAR(p_ready, i), kTile);
-      mbar_init(SPLASH_BAR(epi, i), kTile * AW);
-      mbar_init(SPLASH_BAR(m_ready, i), kTile);
-      mbar_init(SPLASH_BAR(s_free, i), kTile);
-    }
-    mbar_init(SPLASH_BAR(fin, 0), kTile * AW);
-    mbar_init(SPLASH_BAR(pv_done, 0), 1);
-    mbar_init(SPLASH_BAR(pv_done, 1), 1);
-    mbar_init(SPLASH_BAR(o_done, 0), 1);
+    if (lane == 0) sts32(abort_u32, 0);
     fence_mbar_init();
     fence_proxy_async_smem();
-  }
-  __syncthreads();
-  if (lds32(dead_u32)) return;
-  if (warp == kSoftmaxWarps + 1) {
+  } else if (warp == kSoftmaxWarps + 1) {
     tmem_alloc(tmem_slot_u32, L::kTmemCols);
     tmem_relinquish();
   }
@@ -207,6 +196,13 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   tc_fence_after();
   const uint32_t tmem = lds32(tmem_slot_u32);
   const WaitCtx ctx{abort_u32, a.status};
+  if (dead) {
+    if (warp == kSoftmaxWarps + 1) {
+      __syncwarp();
+      tmem_dealloc(tmem, L::kTmemCols);
+    }
+    return;
+  }
 
   constexpr uint32_t kIdescQK = make_idesc(BF16, 128, BKV, false, false);
   constexpr uint32_t kIdescPV = make_idesc(BF16, 128, DV, false, true);
@@ -683,7 +679,7 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             for (int c = 0; c < DV / 64; ++c)
               tma_store_2d(&tm_o, stage + c * (kTile * 128), c * 64, q_row0 + t * kTile);
             bulk_commit_group();
-            bulk_wait_group<0>();
+            bulk_wait_group_read<0>();
           }
         }
       }
