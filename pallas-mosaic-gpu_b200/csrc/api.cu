@@ -123,7 +123,7 @@ extern "C" int64_t splash_bwd_fused_workspace_bytes(const SplashParams* p) {
 extern "C" int splash_bwd_fused(const SplashParams* p, void* stream) {
   if (int rc = check_bwd(p)) return rc;
   if (!p->dq || !p->dk || !p->dv || !p->dq_acc) return fail(SPLASH_INVALID_ARGUMENT, "dq, dk, dv and dq_acc must be non-null");
-  if (p->head_dim != 128) return fail(SPLASH_UNSUPPORTED, "the fused backward is compiled for head_dim 128");
+
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (p->out) {
     // One pass streams O and dO for delta and clears the accumulator on the way.
@@ -133,7 +133,7 @@ extern "C" int splash_bwd_fused(const SplashParams* p, void* stream) {
   } else {
     SPLASH_CUDA_CHECK(cudaMemsetAsync(p->dq_acc, 0, static_cast<size_t>(splash_bwd_fused_workspace_bytes(p)), st));
   }
-  if (int rc = launch_bwd_col<128, true>(*p, st)) return rc;
+  if (int rc = p->head_dim == 64 ? launch_bwd_col<64, true>(*p, st) : launch_bwd_col<128, true>(*p, st)) return rc;
   return launch_dq_transpose_cast(p->dq_acc, p->dq, static_cast<long long>(p->batch) * p->heads, p->head_dim, p->q_len,
                                   p->dtype, st);
 }

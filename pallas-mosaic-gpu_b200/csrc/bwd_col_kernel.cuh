@@ -7,7 +7,7 @@
 //   FUSED = false   dK, dV only (the split backward; dQ comes from bwd_row_kernel).
 //   FUSED = true    also dQ: each step's dQ^T = K^T dS^T tile is reduce-added into an
 //                   f32 accumulator laid out [batch, heads, head_dim, q_len] with a
-//                   TMA add-reduction (head_dim 128, 64 q rows per step).
+//                   TMA add-reduction (64 q rows per step).
 //
 // Per step (64 q rows of one q block):
 //   S^T  = K Q^T        smem x smem -> TMEM f32   [128 kv, 64]
@@ -75,6 +75,11 @@ struct ColLayout {
   static constexpr int kSub = 128 / BC;
   static constexpr int kKBytes = kRows * D * 2;
   static constexpr int kVBytes = kRows * D * 2;
+  // FUSED at head_dim 64: dQ^T = K^T dS^T is issued with M = 128 like at head_dim 128, and
+  // the second 64 rows of its A operand are a second copy of the K tile, so the upper half
+  // of the result repeats the lower half and is simply not stored.  That keeps one
+  // accumulator layout and one writer for both head dims at the price of idle MMA rows.
+  static constexpr int kKDupBytes = (FUSED && D == 64) ? kRows * 128 : 0;
   static constexpr int kQStage = BC * D * 2;
   static constexpr int kDoStage = BC * D * 2;
   static constexpr int kVecStage = BC * 4;          // lse, delta, q segment ids: BC words each
@@ -92,7 +97,7 @@ struct ColLayout {
 
   __host__ __device__ static size_t smem_bytes(int stages, bool dense, bool seg) {
     size_t b = 1024;
-    b += kKBytes + kVBytes;
+    b += kKBytes + kKDupBytes + kVBytes;
     b += static_cast<size_t>(stages) * (kQStage + kDoStage + 2 * kVecStage);
     if (seg) b += static_cast<size_t>(stages) * kVecStage;
     if (dense) b += static_cast<size_t>(stages) * kMaskStage;
@@ -177,7 +182,7 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   extern __shared__ uint8_t smem_raw[];
   const int stages = a.stages;
   const uint32_t k_u32 = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t v_u32 = k_u32 + L::kKBytes;
+  const uint32_t v_u32 = k_u32 + L::kKBytes + L::kKDupBytes;
   const uint32_t q_u32 = v_u32 + L::kVBytes;
   const uint32_t do_u32 = q_u32 + stages * L::kQStage;
   const uint32_t ds_u32 = do_u32 + stages * L::kDoStage;              // FUSED: 2 x dS^T
@@ -250,10 +255,11 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       if (elect_one()) {
         prefetch_tensormap(&tm_q);
         prefetch_tensormap(&tm_do);
-        mbar_arrive_expect_tx(SPLASH_CBAR(kv_full, 0), L::kKBytes + L::kVBytes);
+        mbar_arrive_expect_tx(SPLASH_CBAR(kv_full, 0), L::kKBytes + L::kKDupBytes + L::kVBytes);
 #pragma unroll
         for (int c = 0; c < D / 64; ++c)
           tma_load_2d(k_u32 + c * (kRows * 128), &tm_k, c * 64, kv_row0, SPLASH_CBAR(kv_full, 0));
+        if constexpr (L::kKDupBytes > 0) tma_load_2d(k_u32 + L::kKBytes, &tm_k, 0, kv_row0, SPLASH_CBAR(kv_full, 0));
 #pragma unroll
         for (int c = 0; c < D / 64; ++c)
           tma_load_2d(v_u32 + c * (kRows * 128), &tm_v, c * 64, kv_row0, SPLASH_CBAR(kv_full, 0));
@@ -413,10 +419,12 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           if (leader) bulk_wait_group_read<0>();
           mbar_arrive(SPLASH_CBAR(wr_a, 0));
           if (!warp_wait(SPLASH_CBAR(wr_a, 0), par, ctx, kBSiteWrBarA, t)) { alive = false; break; }
+          if (drow < D) {  // at head_dim 64 the upper rows repeat the lower ones
 #pragma unroll
-          for (int c = 0; c < 8; ++c)
-            sts128(dqs_u32 + swz128(drow, c), make_uint4(acc[half * 32 + c * 4], acc[half * 32 + c * 4 + 1],
-                                                         acc[half * 32 + c * 4 + 2], acc[half * 32 + c * 4 + 3]));
+            for (int c = 0; c < 8; ++c)
+              sts128(dqs_u32 + swz128(drow, c), make_uint4(acc[half * 32 + c * 4], acc[half * 32 + c * 4 + 1],
+                                                           acc[half * 32 + c * 4 + 2], acc[half * 32 + c * 4 + 3]));
+          }
           fence_proxy_async_smem();
           mbar_arrive(SPLASH_CBAR(wr_b, 0));
           if (!warp_wait(SPLASH_CBAR(wr_b, 0), par, ctx, kBSiteWrBarB, t)) { alive = false; break; }

@@ -77,7 +77,7 @@ int launch_bwd_col_typed(const SplashParams& p, cudaStream_t stream) {
   if (FUSED) {
     // f32 accumulator viewed as [batch * heads * head_dim, q_len]; tiles of 32 q columns.
     const uint64_t acc_rows = static_cast<uint64_t>(p.batch) * p.heads * D;
-    if ((rc = make_tmap_2d(&tm_dqacc, p.dq_acc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, acc_rows, p.q_len, 128, 32,
+    if ((rc = make_tmap_2d(&tm_dqacc, p.dq_acc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, acc_rows, p.q_len, D, 32,
                            CU_TENSOR_MAP_SWIZZLE_128B)))
       return rc;
   }

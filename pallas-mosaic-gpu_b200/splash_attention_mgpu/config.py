@@ -158,13 +158,14 @@ def fused_supported(head_dim: int, head_dim_v: int) -> bool:
 
 
 def fused_sub_block(head_dim: int) -> int:
-  """q rows per step of the fused backward: 64 at head_dim 128, 128 at 64."""
-  return 64 if head_dim == 128 else 128
+  """q rows per step of the fused backward (64 at either head dim)."""
+  del head_dim
+  return 64
 
 
 def fused_tmem_cols(head_dim: int) -> int:
-  bc = fused_sub_block(head_dim)
-  return 2 * bc + 2 * head_dim + (head_dim if head_dim == 64 else bc)
+  """Two S^T and two dP^T buffers of 64 columns, dK and dV."""
+  return 4 * fused_sub_block(head_dim) + 2 * head_dim
 
 
 def fused_smem_bytes(*, head_dim, num_stages, itemsize, has_dense_mask,
@@ -172,10 +173,11 @@ def fused_smem_bytes(*, head_dim, num_stages, itemsize, has_dense_mask,
   bc = fused_sub_block(head_dim)
   bkv = TILE_ROWS
   return (bkv * 2 * head_dim * itemsize  # K, V resident
+          + (bkv * 128 if head_dim == 64 else 0)  # second copy of K for the dQ operand
           + num_stages * bc * 2 * head_dim * itemsize  # Q, dO ring
           + num_stages * 2 * bc * 4  # lse, delta
           + 2 * bkv * bc * itemsize  # dS^T staged as an MMA operand, 2 buffers
-          + max(bc * head_dim * 4, 0)  # dQ staging for the reduce-add
+          + 128 * 32 * 4  # dQ^T staging for the reduce-add
           + (num_stages * bkv * bc if has_dense_mask else 0)
           + (bkv + num_stages * bc) * 4 * bool(has_segments))
 

@@ -436,10 +436,12 @@ def _forward(kernel: SplashAttentionKernel, bs: BlockSizes, q, k, v,
 
 def _use_fused_backward(q, v, bs: BlockSizes, has_dense, has_segments) -> bool:
   head_dim = q.shape[-1]
-  # The fused kernel is compiled for head_dim 128 only; head_dim 64 always takes
-  # the split kernels (the reference makes the fused path opt-in there because it
-  # is slower, `splash_attention.py:299-301`).
-  use = head_dim == 128
+  # Head dims 64 and 128.  SPLASH_BWD_FUSED=0 forces the split kernels at any head
+  # dim, SPLASH_BWD_FUSED_D64=0 at head_dim 64 only (the reference makes the fused
+  # path opt-in there because its version is slower, `splash_attention.py:299-301`;
+  # here it is the faster one and on by default).
+  use = head_dim == 128 or (head_dim == 64
+                            and os.environ.get("SPLASH_BWD_FUSED_D64", "1") == "1")
   return bool(
       use and cfg.fused_supported(head_dim, v.shape[-1])
       and cfg.fused_fits(head_dim=head_dim, num_stages=bs.num_stages_bwd,

@@ -65,7 +65,16 @@ GRAD_CASES = [
 
 
 @pytest.mark.parametrize("kwargs", GRAD_CASES, ids=_id)
-def test_gpu_grads(kwargs):
+def test_gpu_grads(kwargs, monkeypatch):
+  # head_dim 64 through the split dQ + dK/dV kernels.
+  monkeypatch.setenv("SPLASH_BWD_FUSED_D64", "0")
+  kwargs = dict(kwargs)
+  _check_grads(kwargs.pop("mask_name"), **kwargs)
+
+
+@pytest.mark.parametrize("kwargs", GRAD_CASES[:12], ids=_id)
+def test_gpu_grads_fused_d64(kwargs):
+  # head_dim 64 through the fused kernel (the default).
   kwargs = dict(kwargs)
   _check_grads(kwargs.pop("mask_name"), **kwargs)
 
