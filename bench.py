@@ -344,9 +344,8 @@ def run_ours(args):
     roofline = dict(bound="tensor", achieved=bwd_tflops, peak=peaks["sustained"], unit="TFLOP/s",
                     frac=bwd_tflops / peaks["sustained"], traffic=630.9e6 if default_wl else None,
                     peak_source=peaks["source"] + " sustained bf16",
-                    kernel="splash_bwd_col_kernel<128,fused> (about 95% of the backward launch group; timed with its "
-                           "delta pass, which also clears the dQ accumulator, and the transpose-cast)" if d == 128 else
-                           "splash_bwd_row_kernel + splash_bwd_col_kernel (+delta)",
+                    kernel=f"splash_bwd_col_kernel<{d},fused> (about 95% of the backward launch group; timed with its "
+                           "delta pass, which also clears the dQ accumulator, and the transpose-cast)",
                     frac_of_nominal_2250=bwd_tflops / 2250.0)
     roofline_fwd = dict(bound="tensor", achieved=fwd_tflops, peak=peaks["sustained"], unit="TFLOP/s",
                         frac=fwd_tflops / peaks["sustained"], traffic=255.0e6 if default_wl else None,
@@ -370,13 +369,13 @@ def run_ours(args):
       cpu = dict(value=val, unit=UNIT, cores=threads, kind="port",
                  sample=f"{n} of {batch * heads} (batch, head) units, dense f32 forward + analytic backward "
                         f"(oracle/dense_attention.py), {sec:.1f} s")
-    launches_per_step = 1 + (3 if d == 128 else 3)  # forward; delta + (fused, cast | dQ, dK/dV)
+    launches_per_step = 1 + 3  # forward; delta (+ accumulator clear), fused backward, transpose-cast
     line = dict(
         metric=METRIC, value=value, unit=UNIT, n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3),
         ms_per_step=ms_per_step, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16" if dt == "bf16" else "f16",
         data="synthetic",
         config=dict(workload=workload, block_q=bs.block_q, block_kv=bs.block_kv, num_stages=bs.num_stages,
-                    backward="fused" if d == 128 else "split", l2="inputs larger than L2 (q,k,v,dO,out,dq,dk,dv "
+                    backward="fused", l2="inputs larger than L2 (q,k,v,dO,out,dq,dk,dv "
                     f"= {8 * batch * heads * seq * d * 2 / 2**20:.0f} MiB per step)",
                     per_rank="every rank runs the whole workload"),
         fwd_tflops=world * fwd_tflops, fwd_ms=fwd_ms, bwd_ms=bwd_ms,
