@@ -1,23 +1,32 @@
 // Splash attention forward for sm_100a: one warp-specialised kernel template that
-// covers both forward variants.
+// covers the forward variants.
 //
-//   NT = 1  one 128-row q tile per CTA.  The two S buffers in tensor memory
-//           alternate between KV steps, so Q.K^T of step s+1 runs while the
-//           softmax warpgroup works on step s.
+//   NT = 1, AW = 1  one 128-row q tile per CTA, one softmax warpgroup.  The two S
+//           buffers in tensor memory alternate between KV steps, so Q.K^T of step
+//           s+1 runs while the warpgroup works on step s.  With 64-wide KV blocks and
+//           a two-stage ring two such CTAs share an SM.
+//   NT = 1, AW = 2  the same tile with two softmax warpgroups that take the KV steps
+//           in turn (128-wide KV blocks).  The groups hand the stale row maximum to
+//           one another through shared memory, keep partial row sums and split the
+//           epilogue; P has tensor-memory columns of its own, so the S buffer of step
+//           s is free as soon as its softmax has read it and Q.K^T of step s+2 runs
+//           under the softmax of step s.
 //   NT = 2  two 128-row q tiles per CTA ("ping-pong").  Each tile has its own S
 //           buffer and its own softmax warpgroup; every K/V block fetched is
 //           used by both tiles, and the tensor core works for one tile while the
 //           other tile's softmax runs.
 //
 // Roles inside a CTA
-//   softmax warpgroup(s)  warps [0, 4*NT): one thread per q row (= TMEM lane)
-//   TMA producer          warp 4*NT, lane 0: Q once, then K, V (+ KV segment ids,
-//                         + the int8 block of a dense partial mask) per visited block
-//   MMA issuer            warp 4*NT+1, lane 0: all tcgen05.mma / commit
+//   softmax warpgroups    warps [0, 4*NT*AW): one thread per q row (= TMEM lane)
+//   K/Q producer          next warp: Q once, then K (+ KV segment ids, + the int8 block
+//                         of a dense partial mask) per visited block
+//   MMA issuer            next warp: all tcgen05.mma / commit, one elected lane
+//   V producer            next warp: V per visited block
 //
 // Data flow per visited KV block:  S = Q K^T (smem x smem -> TMEM f32), softmax in
 // registers (exp2 domain, running max kept stale until it moves by more than 2^8),
-// P written back over S as packed 16-bit, O += P V (TMEM x smem -> TMEM f32).
+// P written to tensor memory as packed 16-bit (over S, or into its own columns with
+// AW = 2), O += P V (TMEM x smem -> TMEM f32).
 // Empty blocks are never touched, FULL blocks skip masking, PARTIAL blocks are
 // masked in registers from a band descriptor or a dense int8 block.
 //
