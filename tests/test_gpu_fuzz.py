@@ -5,6 +5,8 @@ most cases) gradients against the CPU oracle.  Only rows that see at least one k
 compared (tools/fuzz.py:116-124); tolerances are the fuzzer's (3e-2 / 8e-3 output,
 2e-3 lse, 3e-2 gradients)."""
 
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -37,6 +39,8 @@ def _draw(seed):
     bkv = 64
   if c["d"] == 128 and bkv == 128 and stages == 3:
     stages = 2  # does not fit shared memory; the reference's fuzzer skips such draws too
+  if rng.random() < 0.25:
+    bq = bkv = stages = None  # the library's automatic forward tiling
   c["block_sizes"] = sa.BlockSizes(block_q=bq, block_kv=bkv, num_stages=stages,
                                    block_kv_dq=[None, 64, 128][int(rng.integers(3))],
                                    block_q_dkv=[None, 64, 128][int(rng.integers(3))],
@@ -60,7 +64,8 @@ def _one_mask(kind, s, rng):
   return sa.NumpyMask(dense)
 
 
-@pytest.mark.parametrize("seed", range(48))
+# SPLASH_FUZZ_SEEDS=N draws N cases instead of the 48 of a normal run (soak runs).
+@pytest.mark.parametrize("seed", range(int(os.environ.get("SPLASH_FUZZ_SEEDS", "48"))))
 def test_fuzz_case(seed):
   c = _draw(seed)
   rng, s, h, kvh, d = c["rng"], c["seq"], c["heads"], c["kv_heads"], c["d"]
