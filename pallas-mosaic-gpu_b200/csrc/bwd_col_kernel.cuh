@@ -164,7 +164,8 @@ struct ColSteps {
   }
 };
 
-template <int D, bool FUSED, bool BF16>
+// PLAIN: no soft-cap, no segment ids, no streamed mask blocks -- that code is compiled out.
+template <int D, bool FUSED, bool PLAIN, bool BF16>
 __global__ void __launch_bounds__(ColLayout<D, FUSED>::kThreads, 1)
 splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
@@ -179,6 +180,9 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   constexpr int kWriterWarp0 = kEwWarps;                       // FUSED only
   constexpr int kProducerWarp0 = kEwWarps + (FUSED ? 4 : 0);
 
+  const bool has_dense = !PLAIN && a.has_dense;
+  const bool has_seg = !PLAIN && a.has_seg;
+  const float soft_cap = PLAIN ? 0.f : a.soft_cap;
   extern __shared__ uint8_t smem_raw[];
   const int stages = a.stages;
   const uint32_t k_u32 = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -188,10 +192,10 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const uint32_t ds_u32 = do_u32 + stages * L::kDoStage;              // FUSED: 2 x dS^T
   const uint32_t dqs_u32 = ds_u32 + (FUSED ? 2 * L::kDsStage : 0);    // FUSED: dQ^T staging
   const uint32_t mask_u32 = dqs_u32 + (FUSED ? L::kDqStage : 0);
-  const uint32_t lse_u32 = mask_u32 + (a.has_dense ? stages * L::kMaskStage : 0);
+  const uint32_t lse_u32 = mask_u32 + (has_dense ? stages * L::kMaskStage : 0);
   const uint32_t delta_u32 = lse_u32 + stages * L::kVecStage;
   const uint32_t segq_u32 = delta_u32 + stages * L::kVecStage;
-  const uint32_t bars_u32 = (segq_u32 + (a.has_seg ? stages * L::kVecStage : 0) + 15u) & ~15u;
+  const uint32_t bars_u32 = (segq_u32 + (has_seg ? stages * L::kVecStage : 0) + 15u) & ~15u;
   const uint32_t abort_u32 = bars_u32 + static_cast<uint32_t>(offsetof(ColBarriers, abort_flag));
   const uint32_t tmem_slot_u32 = bars_u32 + static_cast<uint32_t>(offsetof(ColBarriers, tmem_base));
 
@@ -271,8 +275,8 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         const int qblk = a.block_list[off];
         const int q_row = (b * a.heads + it.head()) * a.q_len + qblk * 128 + it.sb * BC;
         if (t >= stages && !warp_wait(SPLASH_CBAR(empty, slot), phase ^ 1, ctx, kBSiteTmaEmpty, t)) break;
-        const bool partial_dense = a.has_dense && a.block_kind[off] == SPLASH_BLOCK_PARTIAL;
-        const uint32_t bytes = L::kQStage + L::kDoStage + 2 * L::kVecStage + (a.has_seg ? L::kVecStage : 0) +
+        const bool partial_dense = has_dense && a.block_kind[off] == SPLASH_BLOCK_PARTIAL;
+        const uint32_t bytes = L::kQStage + L::kDoStage + 2 * L::kVecStage + (has_seg ? L::kVecStage : 0) +
                                (partial_dense ? L::kMaskStage : 0);
         const uint32_t bar = SPLASH_CBAR(full, slot);
         const int mrow = partial_dense ? a.mask_block[off] * 128 : 0;
@@ -286,7 +290,7 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             tma_load_2d(do_u32 + slot * L::kDoStage + c * (BC * 128), &tm_do, c * 64, q_row, bar);
           bulk_load_1d(lse_u32 + slot * L::kVecStage, a.lse + q_row, L::kVecStage, bar);
           bulk_load_1d(delta_u32 + slot * L::kVecStage, a.delta + q_row, L::kVecStage, bar);
-          if (a.has_seg)
+          if (has_seg)
             bulk_load_1d(segq_u32 + slot * L::kVecStage,
                          a.seg_q + static_cast<size_t>(b) * a.q_len + qblk * 128 + it.sb * BC, L::kVecStage, bar);
           if (partial_dense) tma_load_2d(mask_u32 + slot * L::kMaskStage, &tm_mask, it.sb * BC, mrow, bar);
@@ -457,9 +461,9 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         for (int c = 0; c < D * 2 / 16; ++c) dst[c] = make_uint4(0, 0, 0, 0);
       }
     } else {
-      const int my_seg = a.has_seg ? a.seg_kv[static_cast<size_t>(b) * a.kv_len + kv_pos] : 0;
-      const bool cap_on = a.soft_cap > 0.f;
-      const float cap = a.soft_cap, inv_cap = cap_on ? 1.f / a.soft_cap : 0.f;
+      const int my_seg = has_seg ? a.seg_kv[static_cast<size_t>(b) * a.kv_len + kv_pos] : 0;
+      const bool cap_on = soft_cap > 0.f;
+      const float cap = soft_cap, inv_cap = cap_on ? 1.f / soft_cap : 0.f;
       bool alive = true;
       int slot = 0;
       uint32_t phase = 0;
@@ -495,7 +499,7 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           tmem_wait_ld();
           uint32_t ppk[16], dspk[16];
           const uint32_t vec_off = slot * L::kVecStage + (col0 + c * 32) * 4;
-          if (!partial && !a.has_seg && !cap_on) {
+          if (!partial && !has_seg && !cap_on) {
             // FULL block, no segment ids, no soft-cap: nothing to mask.  (A row whose lse
             // is mask_value never meets a FULL block, so no guard is needed here.)
 #pragma unroll
@@ -517,7 +521,7 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             }
           } else {
             uint32_t vis = 0xffffffffu;  // bit i: column i of this chunk is visible
-            if (partial && !a.has_dense) {
+            if (partial && !has_dense) {
               const int d0 = kv_pos - (q0 + c * 32);
 #pragma unroll
               for (int i = 0; i < 32; ++i) {
@@ -525,7 +529,7 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 if (d < band_lo || d > band_hi) vis &= ~(1u << i);
               }
             }
-            if (partial && a.has_dense) {
+            if (partial && has_dense) {
               // Transposed block slice: rows = kv, BC bytes per row, TMA-swizzled.
 #pragma unroll
               for (int g = 0; g < 2; ++g) {
@@ -538,7 +542,7 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                   if (((ww[e >> 2] >> ((e & 3) * 8)) & 0xff) == 0) vis &= ~(1u << (g * 16 + e));
               }
             }
-            if (a.has_seg) {
+            if (has_seg) {
 #pragma unroll
               for (int g = 0; g < 8; ++g) {
                 const uint4 sg = lds128(segq_u32 + vec_off + g * 16);

@@ -84,7 +84,9 @@ int launch_bwd_col_typed(const SplashParams& p, cudaStream_t stream) {
   BwdArgs a;
   fill_bwd_args(a, p, dense, seg);
   a.stages = stages;
-  auto kernel = splash_bwd_col_kernel<D, FUSED, BF16>;
+  // The kernel without its soft-cap, segment and streamed-mask code when the call uses none.
+  const bool plain = p.soft_cap == 0.f && !seg && !dense;
+  auto kernel = plain ? splash_bwd_col_kernel<D, FUSED, true, BF16> : splash_bwd_col_kernel<D, FUSED, false, BF16>;
   if ((rc = opt_in_smem(kernel, smem))) return rc;
   const unsigned grid = static_cast<unsigned>(a.kv_blocks) * p.kv_heads * p.batch;
   kernel<<<grid, L::kThreads, smem, stream>>>(tm_q, tm_k, tm_v, tm_do, tm_dk, tm_dv, tm_mask, tm_dqacc, a);

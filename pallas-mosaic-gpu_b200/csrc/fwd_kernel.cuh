@@ -138,7 +138,9 @@ struct FwdBarriers {
 #define SPLASH_BAR(field, idx) \
   (bars_u32 + static_cast<uint32_t>(offsetof(FwdBarriers, field)) + 8u * static_cast<uint32_t>(idx))
 
-template <int D, int DV, int BKV, int NT, int AW, bool BF16>
+// PLAIN: no soft-cap, no segment ids, no streamed mask blocks -- those blocks of the
+// softmax loop are compiled out, which shortens the instruction stream of the common case.
+template <int D, int DV, int BKV, int NT, int AW, bool PLAIN, bool BF16>
 __global__ void __launch_bounds__((NT * AW + 1) * 128, 1)
 splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                   const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
@@ -148,6 +150,9 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   constexpr int kBq = NT * kTile;
   constexpr int kSoftmaxWarps = 4 * NT * AW;
 
+  const bool has_dense = !PLAIN && a.has_dense;
+  const bool has_seg = !PLAIN && a.has_seg;
+  const float soft_cap = PLAIN ? 0.f : a.soft_cap;
   extern __shared__ uint8_t smem_raw[];
   const int stages = a.stages;
   // Shared-window addresses (32-bit) of the buffers; tiles are 1024-byte aligned.
@@ -155,8 +160,8 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const uint32_t k_u32 = q_u32 + L::kQBytes;
   const uint32_t v_u32 = k_u32 + stages * L::kKStage;
   const uint32_t mask_u32 = v_u32 + stages * L::kVStage;
-  const uint32_t seg_u32 = mask_u32 + (a.has_dense ? stages * L::kMaskStage : 0);
-  const uint32_t bars_u32 = seg_u32 + (a.has_seg ? stages * L::kSegStage : 0);
+  const uint32_t seg_u32 = mask_u32 + (has_dense ? stages * L::kMaskStage : 0);
+  const uint32_t bars_u32 = seg_u32 + (has_seg ? stages * L::kSegStage : 0);
   const uint32_t share_u32 = bars_u32 + 1024;  // [row maxima | partial sums of group 0 | of group 1]
   const uint32_t abort_u32 = bars_u32 + static_cast<uint32_t>(offsetof(FwdBarriers, abort_flag));
   const uint32_t tmem_slot_u32 = bars_u32 + static_cast<uint32_t>(offsetof(FwdBarriers, tmem_base));
@@ -172,7 +177,7 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const int mh = a.mask_heads > 1 ? h : 0;
   const int qi = a.block_order[mh * a.q_blocks + order_idx];
   const int n = a.num_steps[mh * a.q_blocks + qi];
-  const bool has_aux = a.has_dense || a.has_seg;
+  const bool has_aux = has_dense || has_seg;
   const int sched_off = (mh * a.q_blocks + qi) * a.max_steps;  // offset into the step lists
   const int q_row0 = (b * a.heads + h) * a.q_len + qi * kBq;   // row in the [B*H*Sq, D] view
 
@@ -252,12 +257,12 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
         if (has_aux) {
           if (s >= stages && !warp_wait(SPLASH_BAR(aux_empty, slot), phase ^ 1, ctx, kSiteTmaAuxEmpty, s)) break;
-          const bool partial_dense = a.has_dense && a.block_kind[sched_off + s] == SPLASH_BLOCK_PARTIAL;
-          const uint32_t bytes = (a.has_seg ? L::kSegStage : 0) + (partial_dense ? L::kMaskStage : 0);
+          const bool partial_dense = has_dense && a.block_kind[sched_off + s] == SPLASH_BLOCK_PARTIAL;
+          const uint32_t bytes = (has_seg ? L::kSegStage : 0) + (partial_dense ? L::kMaskStage : 0);
           const int mrow = partial_dense ? a.mask_block[sched_off + s] * kBq : 0;
           if (elect_one()) {
             mbar_arrive_expect_tx(SPLASH_BAR(aux_full, slot), bytes);
-            if (a.has_seg)
+            if (has_seg)
               bulk_load_1d(seg_u32 + slot * L::kSegStage, a.seg_kv + static_cast<size_t>(b) * a.kv_len + j * BKV,
                            L::kSegStage, SPLASH_BAR(aux_full, slot));
             if (partial_dense) {
@@ -449,7 +454,7 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           band_hi = min(band_hi, start + chunk - 1 - q_pos);
         }
       }
-      const int my_seg = a.has_seg ? a.seg_q[static_cast<size_t>(b) * a.q_len + q_pos] : 0;
+      const int my_seg = has_seg ? a.seg_q[static_cast<size_t>(b) * a.q_len + q_pos] : 0;
 
       float m_run = -INFINITY;  // stale running max, raw logit units
       float l_run = 0.f;
@@ -485,8 +490,8 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           tc_fence_before();
           mbar_arrive(SPLASH_BAR(s_free, buf));
         }
-        if (a.soft_cap > 0.f) {
-          const float cap = a.soft_cap, inv_cap = 1.f / a.soft_cap;
+        if (soft_cap > 0.f) {
+          const float cap = soft_cap, inv_cap = 1.f / soft_cap;
 #pragma unroll
           for (int i = 0; i < BKV; ++i) sv[i] = cap * tanh_approx(sv[i] * inv_cap);
         }
@@ -494,7 +499,7 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           if (!warp_wait(SPLASH_BAR(aux_full, slot), phase, ctx, kSiteSmxAux, s)) { alive = false; break; }
         }
         const bool partial = kind_now == SPLASH_BLOCK_PARTIAL;
-        if (partial && !a.has_dense) {
+        if (partial && !has_dense) {
           const int d0 = j_now * BKV - q_pos;
 #pragma unroll
           for (int i = 0; i < BKV; ++i) {
@@ -502,7 +507,7 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             if (d < band_lo || d > band_hi) sv[i] = -INFINITY;
           }
         }
-        if (partial && a.has_dense) {
+        if (partial && has_dense) {
           const uint32_t mrow = mask_u32 + slot * L::kMaskStage + t * (kTile * BKV);
 #pragma unroll
           for (int c = 0; c < BKV / 16; ++c) {
@@ -515,7 +520,7 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
               if (((ww[e >> 2] >> ((e & 3) * 8)) & 0xff) == 0) sv[c * 16 + e] = -INFINITY;
           }
         }
-        if (a.has_seg) {
+        if (has_seg) {
           const uint32_t segs = seg_u32 + slot * L::kSegStage;
 #pragma unroll
           for (int c = 0; c < BKV / 4; ++c) {
@@ -603,7 +608,7 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             tmem_st16(p_tmem + c * 16, pk);
           }
         };
-        if (kEmuPairs > 0 && !partial && !a.has_seg) exp_row(std::integral_constant<int, kEmuPairs>{});
+        if (kEmuPairs > 0 && !partial && !has_seg) exp_row(std::integral_constant<int, kEmuPairs>{});
         else exp_row(std::integral_constant<int, 0>{});
         l_run += (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
 

@@ -10,8 +10,8 @@
 
 namespace splash {
 
-template <int D, int DV, int BKV, int NT, int AW, bool BF16>
-int launch_fwd_typed(const SplashParams& p, cudaStream_t stream) {
+template <int D, int DV, int BKV, int NT, int AW, bool PLAIN, bool BF16>
+int launch_fwd_plain(const SplashParams& p, cudaStream_t stream) {
   using L = FwdLayout<D, DV, BKV, NT, AW>;
   const bool dense = p.partial_blocks != nullptr;
   const bool seg = p.seg_q != nullptr;
@@ -68,12 +68,20 @@ int launch_fwd_typed(const SplashParams& p, cudaStream_t stream) {
   a.mask_value = p.mask_value;
   a.soft_cap = p.soft_cap;
 
-  auto kernel = splash_fwd_kernel<D, DV, BKV, NT, AW, BF16>;
+  auto kernel = splash_fwd_kernel<D, DV, BKV, NT, AW, PLAIN, BF16>;
   if ((rc = opt_in_smem(kernel, smem))) return rc;
   const unsigned grid = static_cast<unsigned>(a.q_blocks) * p.heads * p.batch;
   kernel<<<grid, L::kThreads, smem, stream>>>(tm_q, tm_k, tm_v, tm_o, tm_mask, a);
   SPLASH_CUDA_CHECK(cudaGetLastError());
   return SPLASH_OK;
+}
+
+// The kernel without its soft-cap, segment and streamed-mask code when the call uses none.
+template <int D, int DV, int BKV, int NT, int AW, bool BF16>
+int launch_fwd_typed(const SplashParams& p, cudaStream_t stream) {
+  const bool plain = p.soft_cap == 0.f && p.seg_q == nullptr && p.partial_blocks == nullptr;
+  if (plain) return launch_fwd_plain<D, DV, BKV, NT, AW, true, BF16>(p, stream);
+  return launch_fwd_plain<D, DV, BKV, NT, AW, false, BF16>(p, stream);
 }
 
 // Softmax warpgroups that alternate over the KV steps of a one-tile kernel;
