@@ -132,7 +132,7 @@ splash_bwd_row_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = lds32(tmem_slot_u32);
-  const WaitCtx ctx{abort_u32, a.status};
+  const WaitCtx ctx{abort_u32};
   constexpr uint32_t kDescHi = desc_hi(1024);
 
   if (warp >= kEwWarps) {
@@ -386,7 +386,8 @@ splash_bwd_row_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 
   tc_fence_before();
   __syncthreads();
-  if (lds32(abort_u32)) {
+  if (const uint32_t gave_up = lds32(abort_u32)) {
+    if (threadIdx.x == 0) report_abort(a.status, gave_up);
     const uint64_t t0 = global_timer_ns();
     while (global_timer_ns() - t0 < 200000) {}
   }

@@ -209,7 +209,7 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = lds32(tmem_slot_u32);
-  const WaitCtx ctx{abort_u32, a.status};
+  const WaitCtx ctx{abort_u32};
   if (dead) {
     if (warp == kSoftmaxWarps + 1) {
       __syncwarp();
@@ -703,7 +703,8 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   // ---- teardown: every thread of every role ends up here --------------------------
   tc_fence_before();
   __syncthreads();
-  if (lds32(abort_u32)) {
+  if (const uint32_t gave_up = lds32(abort_u32)) {
+    if (threadIdx.x == 0) report_abort(a.status, gave_up);
     // Give copies that were still in flight time to land before the CTA's shared
     // memory is handed to another CTA.
     const uint64_t t0 = global_timer_ns();

@@ -68,10 +68,13 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 
-// Context every role carries for bounded waits.
+// Context every role carries for bounded waits: the shared-window address of one
+// word per CTA.  Zero while all is well; a waiter that gives up stores its wait site
+// and step there, every other waiter of the CTA then returns too, and the kernel's
+// teardown copies the word to the global status record once.  Keeping the report out
+// of the waits keeps the instruction stream of the hot loops short.
 struct WaitCtx {
-  uint32_t cta_abort;  // shared-window address of a flag: some role of this CTA gave up
-  int* status;         // global status word
+  uint32_t cta_abort;
 };
 
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
@@ -121,17 +124,21 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
     if ((++spins & 0xff) == 0) {
       if (lds32(ctx.cta_abort)) return false;
       if (global_timer_ns() - t0 > kWaitLimitNs) {
-        sts32(ctx.cta_abort, 1);
-        if (atomicCAS(ctx.status, 0, kDevWaitTimeout) == 0) {
-          ctx.status[1] = site;
-          ctx.status[2] = static_cast<int>(blockIdx.x);
-          ctx.status[3] = step;
-        }
-        __threadfence();
+        sts32(ctx.cta_abort, 0x80000000u | (static_cast<uint32_t>(site) << 20) | (static_cast<uint32_t>(step) & 0xfffffu));
         return false;
       }
     }
   }
+}
+
+// Teardown: one thread publishes what a waiter of this CTA stored (first CTA wins).
+__device__ __forceinline__ void report_abort(int* status, uint32_t word) {
+  if (atomicCAS(status, 0, kDevWaitTimeout) == 0) {
+    status[1] = static_cast<int>((word >> 20) & 0x7ffu);
+    status[2] = static_cast<int>(blockIdx.x);
+    status[3] = static_cast<int>(word & 0xfffffu);
+  }
+  __threadfence();
 }
 
 // Whole-warp wait with a warp-uniform verdict, for warps that go on to execute

@@ -41,7 +41,7 @@ selftest_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = bars->tmem_base;
-  WaitCtx ctx{smem_u32(&bars->abort_flag), status};
+  WaitCtx ctx{smem_u32(&bars->abort_flag)};
   const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
   const int row = warp * 32 + lane;
   const uint32_t a_tmem_col = 256;  // A operand columns when staged in tensor memory
@@ -62,7 +62,11 @@ selftest_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
   __syncthreads();
   tc_fence_after();
 
-  if (threadIdx.x == 0) {
+  if (a_mode == 3) {
+    // Wait-limit check: nothing ever arrives on this barrier, so the bounded wait runs
+    // out (about a second), records site 102 / step 7 and the kernel unwinds normally.
+    if (warp == 0) warp_wait(smem_u32(&bars->full), 0, ctx, 102, 7);
+  } else if (threadIdx.x == 0) {
     uint32_t bytes = n * kd * 2 + (a_mode == 2 ? 0 : 128 * kd * 2);
     const uint32_t full = smem_u32(&bars->full);
     mbar_arrive_expect_tx(full, bytes);
@@ -101,7 +105,7 @@ selftest_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
     }
   }
   __syncwarp();
-  if (warp_wait(smem_u32(&bars->done), 0, ctx, 101, 0)) {
+  if (a_mode != 3 && warp_wait(smem_u32(&bars->done), 0, ctx, 101, 0)) {
     tc_fence_after();
     for (int c = 0; c < n / 16; ++c) {
       uint32_t r[16];
@@ -113,6 +117,7 @@ selftest_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
   }
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0 && bars->abort_flag) report_abort(status, static_cast<uint32_t>(bars->abort_flag));
   if (warp == 0) {
     __syncwarp();
     tc_fence_after();
@@ -127,11 +132,11 @@ extern "C" int splash_selftest_umma(const void* a, const void* b, float* d, int3
   using namespace splash;
   if (!a || !b || !d || !status) return fail(SPLASH_INVALID_ARGUMENT, "null pointer");
   if (n % 64 || n < 64 || n > 256 || kd % 64 || kd < 64 || kd > 256) return fail(SPLASH_INVALID_ARGUMENT, "n, kd must be multiples of 64 in [64, 256]");
-  if (a_mode < 0 || a_mode > 2 || b_mode < 0 || b_mode > 1) return fail(SPLASH_INVALID_ARGUMENT, "bad operand mode");
+  if (a_mode < 0 || a_mode > 3 || b_mode < 0 || b_mode > 1) return fail(SPLASH_INVALID_ARGUMENT, "bad operand mode");
   const CUtensorMapDataType dt = tmap_dtype(dtype);
   CUtensorMap tm_a, tm_b;
   int rc;
-  if (a_mode == 1) rc = make_tmap_2d(&tm_a, a, dt, 2, kd, 128, kd, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (a_mode == 1) rc = make_tmap_2d(&tm_a, a, dt, 2, kd, 128, kd, 64, CU_TENSOR_MAP_SWIZZLE_128B);  // a_mode 3 (wait-limit check) never loads
   else rc = make_tmap_2d(&tm_a, a, dt, 2, 128, kd, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc) return rc;
   if (b_mode == 1) rc = make_tmap_2d(&tm_b, b, dt, 2, kd, n, kd, 64, CU_TENSOR_MAP_SWIZZLE_128B);

@@ -33,3 +33,21 @@ def test_umma_selftest(a_mode, b_mode, n, kd, dtype):
   torch.cuda.synchronize()
   assert status.tolist() == [0, 0, 0, 0], f"device status {status.tolist()}"
   np.testing.assert_allclose(d.cpu().numpy(), want.cpu().numpy(), atol=2e-2, rtol=1e-3)
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_context_survives():
+  # Mode 3 of the self-test waits on a barrier nothing arrives on: the bounded wait gives
+  # up after about a second, the kernel unwinds, and the status word names the wait.
+  lib = _ffi.load()
+  status = torch.zeros(4, dtype=torch.int32, device="cuda:0")
+  a_in = torch.zeros(128, 64, dtype=torch.bfloat16, device="cuda:0")
+  b_in = torch.zeros(64, 64, dtype=torch.bfloat16, device="cuda:0")
+  d = torch.zeros(128, 64, dtype=torch.float32, device="cuda:0")
+  rc = lib.splash_selftest_umma(a_in.data_ptr(), b_in.data_ptr(), d.data_ptr(), 64, 64, 3, 0, _ffi.DTYPE_BF16,
+                                status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+  _ffi.check(rc, "selftest")
+  torch.cuda.synchronize()
+  assert status.cpu().tolist() == [1, 102, 0, 7]
+  # The device is still usable: an ordinary self-test on a fresh status word passes.
+  status.zero_()
+  test_umma_selftest(0, 0, 64, 64, torch.bfloat16)
