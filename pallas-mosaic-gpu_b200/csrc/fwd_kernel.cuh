@@ -620,7 +620,9 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
         if (s > 0 && __any_sync(0xffffffffu, moved)) {
           tc_fence_after();
-#pragma unroll
+          // Rare after the first steps: kept as a rolled loop so that it does not pad the
+          // instruction stream of the common case.
+#pragma unroll 1
           for (int c = 0; c < DV / 32; ++c) {
             uint32_t o[32];
             tmem_ld32(o_tmem + c * 32, o);
