@@ -36,7 +36,6 @@
 
 #include <stddef.h>
 
-#include <type_traits>
 
 #include "../../include/splash_sm100.h"
 #include "ptx.cuh"
@@ -46,10 +45,6 @@ namespace splash {
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;  // in powers of two
-#ifndef SPLASH_EMU_PAIRS
-#define SPLASH_EMU_PAIRS 0
-#endif
-constexpr int kEmuPairs = SPLASH_EMU_PAIRS;  // of every 8 element pairs, how many use the polynomial exp2
 
 struct FwdArgs {
   const int32_t* num_steps;
@@ -582,34 +577,22 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const float m_scaled = (m_run == -INFINITY) ? 0.f : m_run * kLog2e;
         const float2 scale2 = make_float2(kLog2e, kLog2e), shift2 = make_float2(-m_scaled, -m_scaled);
         float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
-        // P goes over the S it came from, 32 columns of S (16 packed words) at a time so
-        // that only one small staging group is live beside the row itself.  In blocks with
-        // nothing masked, kEmuPairs of every 8 element pairs take the polynomial exp2 (FMA
-        // pipe) instead of ex2.approx (special function unit), the unit this loop
-        // saturates.  The two variants are separate straight-line loops on purpose.
-        auto exp_row = [&](auto emu_tag) {
-          constexpr int kEmu = decltype(emu_tag)::value;
+        // P is packed 32 columns of S (16 words) at a time, so that only one small staging
+        // group is live beside the row itself.
 #pragma unroll
-          for (int c = 0; c < BKV / 32; ++c) {
-            uint32_t pk[16];
+        for (int c = 0; c < BKV / 32; ++c) {
+          uint32_t pk[16];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const float2 x = fma2(make_float2(sv[c * 32 + 2 * j], sv[c * 32 + 2 * j + 1]), scale2, shift2);
-              float2 pr;
-              if ((j & 7) >= 8 - kEmu) {
-                pr = ex2_poly2(x);
-              } else {
-                pr.x = ex2_approx(x.x);
-                pr.y = ex2_approx(x.y);
-              }
-              if (j & 1) sum_b = add2(sum_b, pr); else sum_a = add2(sum_a, pr);
-              pk[j] = pack2<BF16>(pr.x, pr.y);
-            }
-            tmem_st16(p_tmem + c * 16, pk);
+          for (int j = 0; j < 16; ++j) {
+            const float2 x = fma2(make_float2(sv[c * 32 + 2 * j], sv[c * 32 + 2 * j + 1]), scale2, shift2);
+            float2 pr;
+            pr.x = ex2_approx(x.x);
+            pr.y = ex2_approx(x.y);
+            if (j & 1) sum_b = add2(sum_b, pr); else sum_a = add2(sum_a, pr);
+            pk[j] = pack2<BF16>(pr.x, pr.y);
           }
-        };
-        if (kEmuPairs > 0 && !partial && !has_seg) exp_row(std::integral_constant<int, kEmuPairs>{});
-        else exp_row(std::integral_constant<int, 0>{});
+          tmem_st16(p_tmem + c * 16, pk);
+        }
         l_run += (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
 
         // O may only be touched once P.V of the previous step has finished.  With two

@@ -487,29 +487,6 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return d;
 }
 
-// 2^x for a pair of finite x <= ~100 on the FMA / integer pipes, leaving the special
-// function unit free: x is split into an integer n (round to nearest, by adding
-// 1.5 * 2^23) and f = x - n in [-0.5, 0.5]; 2^f comes from a cubic fitted on that
-// interval (maximum relative error 7.5e-5, far below the 16-bit precision P is stored
-// in) and n is added into the exponent field.  x is clamped at -126 so the exponent
-// cannot wrap; the result for such x is ~1e-38 rather than 0, so callers must not use
-// this for masked (-inf) entries.
-__device__ __forceinline__ float2 ex2_poly2(float2 x) {
-  const float kMagic = 12582912.0f;  // 1.5 * 2^23
-  x.x = fmaxf(x.x, -126.f);
-  x.y = fmaxf(x.y, -126.f);
-  const float2 t = add2(x, make_float2(kMagic, kMagic));
-  const float2 n = add2(t, make_float2(-kMagic, -kMagic));
-  const float2 f = fma2(n, make_float2(-1.f, -1.f), x);
-  float2 p = fma2(make_float2(0.0551716685f, 0.0551716685f), f, make_float2(0.242611125f, 0.242611125f));
-  p = fma2(p, f, make_float2(0.693260968f, 0.693260968f));
-  p = fma2(p, f, make_float2(0.999928057f, 0.999928057f));
-  float2 r;
-  r.x = __int_as_float(__float_as_int(t.x) * 8388608 + __float_as_int(p.x));
-  r.y = __int_as_float(__float_as_int(t.y) * 8388608 + __float_as_int(p.y));
-  return r;
-}
-
 // Packs two f32 into one 32-bit register of two 16-bit floats; `lo` lands in the
 // low half (the lower-indexed element).
 template <bool kBf16>
