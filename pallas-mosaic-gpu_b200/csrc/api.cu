@@ -1,5 +1,7 @@
 // extern "C" entry points of libsplash_sm100.so: argument validation, dispatch to
 // the compiled kernel configuration, status helpers.
+#include <cstdlib>
+
 #include "dispatch.h"
 #include "host_common.cuh"
 
@@ -133,7 +135,14 @@ extern "C" int splash_bwd_fused(const SplashParams* p, void* stream) {
   } else {
     SPLASH_CUDA_CHECK(cudaMemsetAsync(p->dq_acc, 0, static_cast<size_t>(splash_bwd_fused_workspace_bytes(p)), st));
   }
-  if (int rc = p->head_dim == 64 ? launch_bwd_col<64, true>(*p, st) : launch_bwd_col<128, true>(*p, st)) return rc;
+  // Head dim 128 takes the kernel that works on whole 128-row q blocks; streamed mask blocks
+  // and head dim 64 take the 64-row one.  SPLASH_BWD_WIDE=0 forces the latter (experiments).
+  const char* wide_env = getenv("SPLASH_BWD_WIDE");
+  const bool wide_off = wide_env && wide_env[0] == '0';
+  int rc;
+  if (!wide_off && bwd_wide_supported(*p)) rc = launch_bwd_wide(*p, st);
+  else rc = p->head_dim == 64 ? launch_bwd_col<64, true>(*p, st) : launch_bwd_col<128, true>(*p, st);
+  if (rc) return rc;
   return launch_dq_transpose_cast(p->dq_acc, p->dq, static_cast<long long>(p->batch) * p->heads, p->head_dim, p->q_len,
                                   p->dtype, st);
 }

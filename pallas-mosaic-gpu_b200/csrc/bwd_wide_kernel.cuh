@@ -1,0 +1,574 @@
+// Splash attention fused backward over the column (per-KV-block) schedule with 128 q
+// rows per step, head_dim 128, sm_100a.
+//
+// Why a second column kernel.  The 64-row-per-step kernel (bwd_col_kernel.cuh) is bound
+// by the shared-memory data pipe, not by the tensor core: a tcgen05.mma that reads both
+// operands from shared memory streams M x 16 + N x 16 16-bit values per instruction, and
+// with N = 64 that is 6 KB for 32 cycles of arithmetic -- more than the 128 bytes per
+// cycle the pipe delivers.  Taking a whole 128-row q block per step makes every
+// score-shaped product N = 128 (8 KB for 64 cycles: exactly the pipe's rate) and reads
+// the stationary K / V tile once per 128 q rows instead of twice; shared-memory traffic
+// per visited block pair drops by about a quarter.
+//
+// One CTA owns one 128-row KV block of one KV head and walks every q block that sees it,
+// for every q head of the KV head's group (GQA/MQA heads are reduced in tensor memory).
+// Per step (one 128 x 128 block pair):
+//   S^T  = K Q^T        smem x smem -> TMEM region R1 (f32, 128 columns)
+//   dP^T = V dO^T       smem x smem -> TMEM region R2
+//   phase A (needs S^T):   P^T = exp2((S^T - lse) log2e), packed 16-bit over R1
+//   phase B (needs dP^T):  dS^T = P^T (dP^T - delta) [(1 - tanh^2) with soft-cap], packed
+//                          over R2 and staged in shared memory as an MMA operand
+//   dV  += P^T dO       TMEM x smem
+//   dK  += dS^T Q       TMEM x smem
+//   dQ^T = K^T dS^T     smem x smem -> R2, drained by a writer warpgroup that
+//                       reduce-adds it into the f32 accumulator [batch*heads*128, q_len]
+//
+// Tensor memory holds R1, R2, dK and dV (4 x 128 = 512 columns), so the scores are not
+// double-buffered; the overlap comes from the issue order instead:
+//   dP^T(t)  dV(t)  S^T(t+1)  dK(t)  dQ^T(t)  [writer drains R2]  dP^T(t+1) ...
+// Phase B of step t runs under dV(t) and S^T(t+1); phase A of step t+1 runs under dK(t),
+// dQ^T(t), the drain and dP^T(t+1).  The only gap in the tensor core's queue is the drain
+// of R2.  Q has two slots (Q(t) lives from S^T(t) to dK(t), across S^T(t+1)); dO has one
+// (it lives from dP^T(t) to dV(t), which are adjacent) and is refilled under S^T(t+1),
+// dK(t) and dQ^T(t).  The writer stages f32 dQ^T tiles in 32 KB of its own, so it only
+// has to keep up with the step rate.
+//
+// Behaviour follows the reference kernel (splash_attention_mgpu/backward_fused.py:64-512);
+// the code shares nothing with it.
+#pragma once
+
+#include <stddef.h>
+
+#include "bwd_col_kernel.cuh"  // BwdArgs, ColSteps, math constants
+#include "ptx.cuh"
+
+namespace splash {
+
+enum WideSite : int {
+  kWSiteQEmpty = 61, kWSiteDoEmpty, kWSiteMmaKV, kWSiteMmaQ, kWSiteMmaDo, kWSiteMmaP, kWSiteMmaDs, kWSiteMmaDqFree,
+  kWSiteEwQ, kWSiteEwS, kWSiteEwDp, kWSiteEwStage, kWSiteEwDone, kWSiteEwEpi,
+  kWSiteWrReady, kWSiteWrBarA, kWSiteWrBarB,
+};
+
+struct WideLayout {
+  static constexpr int D = 128;
+  static constexpr int kRows = 128;  // kv rows per CTA
+  static constexpr int BC = 128;     // q rows per step
+  static constexpr int kTile = kRows * D * 2;  // every 16-bit tile here is 32 KB
+  static constexpr int kBox = kRows * 128;     // one 64-element-wide box of a tile
+  static constexpr int kSlots = 2;
+  static constexpr int kVecBytes = BC * 4;
+  // Shared memory map (bytes from the 1024-aligned base).
+  static constexpr int kOffK = 0, kOffV = kTile, kOffQ = 2 * kTile, kOffDo = 4 * kTile, kOffDs = 5 * kTile;
+  static constexpr int kOffDqStage = 6 * kTile;  // two f32 tiles of [128 d, 32 q]
+  static constexpr int kOffLse = 7 * kTile, kOffDelta = kOffLse + kSlots * kVecBytes;
+  static constexpr int kOffBars = kOffDelta + kSlots * kVecBytes;
+  static constexpr int kBarBytes = 256;
+  static constexpr int kSmemBytes = kOffBars + kBarBytes;
+  // Tensor memory columns.
+  static constexpr int kColS = 0, kColDp = 128, kColDk = 256, kColDv = 384;
+  static constexpr int kTmemCols = 512;
+  static constexpr int kEwThreads = 256;
+  static constexpr int kThreads = 512;  // 2 elementwise warpgroups, writer warpgroup, producer warpgroup
+  // Registers per thread after the warpgroups have traded: 256 * 160 + 128 * 152 + 128 * 40 = 64 K.
+  static constexpr int kEwRegs = 160, kWriterRegs = 152, kProducerRegs = 40;
+};
+
+struct WideBarriers {
+  uint64_t kv_full;
+  uint64_t q_full[2], q_empty[2], do_full, do_empty;
+  uint64_t s_ready, dp_ready, p_ready, ds_ready;
+  uint64_t dq_ready, dq_free, wr_a, wr_b;
+  uint64_t acc_done, epi[2];
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+  uint32_t dead;
+};
+static_assert(sizeof(WideBarriers) <= WideLayout::kBarBytes, "barrier block");
+
+#define SPLASH_WBAR(field, idx) \
+  (bars_u32 + static_cast<uint32_t>(offsetof(WideBarriers, field)) + 8u * static_cast<uint32_t>(idx))
+
+// PLAIN: no soft-cap and no segment ids -- that code is compiled out.  Streamed (dense
+// int8) mask blocks are not handled here; calls that carry them take the 64-row kernel.
+template <bool PLAIN, bool BF16>
+__global__ void __launch_bounds__(WideLayout::kThreads, 1)
+splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+                       const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv,
+                       const __grid_constant__ CUtensorMap tm_dqacc, const BwdArgs a) {
+  using L = WideLayout;
+  constexpr int D = L::D;
+  constexpr int kRows = L::kRows;
+  constexpr int kEwWarps = 8;
+  constexpr int kWriterWarp0 = 8;
+  constexpr int kProducerWarp0 = 12;  // +0 Q/K/V producer, +1 MMA issuer, +2 dO producer
+
+  const bool has_seg = !PLAIN && a.has_seg;
+  const float soft_cap = PLAIN ? 0.f : a.soft_cap;
+  extern __shared__ __align__(1024) uint8_t smem_wide[];
+  const uint32_t base_u32 = smem_u32(smem_wide);
+  const uint32_t k_u32 = base_u32 + L::kOffK;
+  const uint32_t v_u32 = base_u32 + L::kOffV;
+  const uint32_t q_u32 = base_u32 + L::kOffQ;
+  const uint32_t do_u32 = base_u32 + L::kOffDo;
+  const uint32_t ds_u32 = base_u32 + L::kOffDs;
+  const uint32_t dqs_u32 = base_u32 + L::kOffDqStage;
+  const uint32_t lse_u32 = base_u32 + L::kOffLse;
+  const uint32_t delta_u32 = base_u32 + L::kOffDelta;
+  const uint32_t bars_u32 = base_u32 + L::kOffBars;
+  const uint32_t abort_u32 = bars_u32 + static_cast<uint32_t>(offsetof(WideBarriers, abort_flag));
+  const uint32_t dead_u32 = bars_u32 + static_cast<uint32_t>(offsetof(WideBarriers, dead));
+  const uint32_t tmem_slot_u32 = bars_u32 + static_cast<uint32_t>(offsetof(WideBarriers, tmem_base));
+
+  const int warp = uniform_warp_index();
+  const int lane = threadIdx.x & 31;
+
+  // ---- which KV block ----------------------------------------------------------
+  const int group = a.heads / a.kv_heads;
+  int hb, order_idx;
+  decode_work_item(blockIdx.x, a.kv_blocks, a.kv_heads * a.batch, a.head_group, hb, order_idx);
+  const int kvh = hb % a.kv_heads;
+  const int b = hb / a.kv_heads;
+  const int head0 = kvh * group;
+  const int mh0 = a.mask_heads > 1 ? head0 : 0;
+  const int kj = a.block_order[mh0 * a.kv_blocks + order_idx];
+  const int kv_row0 = (b * a.kv_heads + kvh) * a.kv_len + kj * kRows;  // row in the [B*KVH*Skv, D] view
+
+  ColSteps<1> it;
+  it.init(&a, kj, head0, group);
+  const int total = it.total();
+
+  // One warp initialises the barriers while the MMA warp allocates tensor memory.  Thread
+  // 0 reads the status word once and shares it, so the whole CTA agrees on whether an
+  // earlier launch already gave up; the tiles need a 1024-byte aligned base, which the
+  // same thread checks.
+  if (warp == 0) {
+    constexpr uint32_t kNumBarriers = offsetof(WideBarriers, tmem_base) / 8;
+    for (uint32_t i = lane; i < kNumBarriers; i += 32) {
+      const uint32_t off = 8u * i;
+      uint32_t count = 1;
+      if (off >= offsetof(WideBarriers, q_empty) && off < offsetof(WideBarriers, do_full)) count = 1 + kEwWarps;  // dK + vector readers
+      if (off == offsetof(WideBarriers, p_ready) || off == offsetof(WideBarriers, ds_ready)) count = L::kEwThreads;
+      if (off == offsetof(WideBarriers, dq_free) || off == offsetof(WideBarriers, wr_a) ||
+          off == offsetof(WideBarriers, wr_b) || off >= offsetof(WideBarriers, epi))
+        count = 128;
+      mbar_init(bars_u32 + off, count);
+    }
+    if (lane == 0) {
+      sts32(abort_u32, 0);
+      uint32_t dead_word = a.status[0] != 0;
+      if (base_u32 & 1023u) {
+        if (atomicCAS(a.status, 0, kDevBadSchedule) == 0) {
+          a.status[1] = 0;
+          a.status[2] = static_cast<int>(blockIdx.x);
+          a.status[3] = static_cast<int>(base_u32 & 1023u);
+        }
+        dead_word = 1;
+      }
+      sts32(dead_u32, dead_word);
+    }
+    fence_mbar_init();
+    fence_proxy_async_smem();
+  } else if (warp == kProducerWarp0 + 1) {
+    tmem_alloc(tmem_slot_u32, L::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = lds32(tmem_slot_u32);
+  const WaitCtx ctx{abort_u32};
+  if (lds32(dead_u32)) {
+    if (warp == kProducerWarp0 + 1) {
+      __syncwarp();
+      tmem_dealloc(tmem, L::kTmemCols);
+    }
+    return;
+  }
+  constexpr uint32_t kDescHi = desc_hi(1024);
+
+  if (warp >= kProducerWarp0) {
+    setmaxnreg_dec<L::kProducerRegs>();
+    if (warp == kProducerWarp0 && total > 0) {
+      // -------------------- K, V once; then the Q ring (with lse, delta) --------------------
+      if (elect_one()) {
+        prefetch_tensormap(&tm_q);
+        prefetch_tensormap(&tm_k);
+        prefetch_tensormap(&tm_v);
+        mbar_arrive_expect_tx(SPLASH_WBAR(kv_full, 0), 2 * L::kTile);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) tma_load_2d(k_u32 + c * L::kBox, &tm_k, c * 64, kv_row0, SPLASH_WBAR(kv_full, 0));
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) tma_load_2d(v_u32 + c * L::kBox, &tm_v, c * 64, kv_row0, SPLASH_WBAR(kv_full, 0));
+      }
+      for (int t = 0; it.valid(); it.next(), ++t) {
+        const int slot = t & 1;
+        const int qblk = a.block_list[it.off()];
+        const int q_row = (b * a.heads + it.head()) * a.q_len + qblk * 128;
+        if (t >= 2 && !warp_wait(SPLASH_WBAR(q_empty, slot), ((t >> 1) & 1) ^ 1, ctx, kWSiteQEmpty, t)) break;
+        if (elect_one()) {
+          const uint32_t bar = SPLASH_WBAR(q_full, slot);
+          mbar_arrive_expect_tx(bar, L::kTile + 2 * L::kVecBytes);
+#pragma unroll
+          for (int c = 0; c < D / 64; ++c) tma_load_2d(q_u32 + slot * L::kTile + c * L::kBox, &tm_q, c * 64, q_row, bar);
+          bulk_load_1d(lse_u32 + slot * L::kVecBytes, a.lse + q_row, L::kVecBytes, bar);
+          bulk_load_1d(delta_u32 + slot * L::kVecBytes, a.delta + q_row, L::kVecBytes, bar);
+        }
+      }
+    } else if (warp == kProducerWarp0 + 2 && total > 0) {
+      // ------------------------------------ dO ring ------------------------------------
+      if (elect_one()) prefetch_tensormap(&tm_do);
+      for (int t = 0; it.valid(); it.next(), ++t) {
+        const int qblk = a.block_list[it.off()];
+        const int q_row = (b * a.heads + it.head()) * a.q_len + qblk * 128;
+        if (t >= 1 && !warp_wait(SPLASH_WBAR(do_empty, 0), (t & 1) ^ 1, ctx, kWSiteDoEmpty, t)) break;
+        if (elect_one()) {
+          const uint32_t bar = SPLASH_WBAR(do_full, 0);
+          mbar_arrive_expect_tx(bar, L::kTile);
+#pragma unroll
+          for (int c = 0; c < D / 64; ++c) tma_load_2d(do_u32 + c * L::kBox, &tm_do, c * 64, q_row, bar);
+        }
+      }
+    } else if (warp == kProducerWarp0 + 1 && total > 0) {
+      // ----------------------------------- MMA issuer -----------------------------------
+      // All lanes run the loop; one elected lane issues each instruction.
+      constexpr uint32_t kIdescScore = make_idesc(BF16, 128, 128, false, false);  // K Q^T, V dO^T
+      constexpr uint32_t kIdescAcc = make_idesc(BF16, 128, D, false, true);        // P^T dO, dS^T Q
+      constexpr uint32_t kIdescDq = make_idesc(BF16, 128, 128, true, true);        // K^T dS^T
+      // K-major tiles: 64-element boxes side by side, 32 bytes per 16-element slice.
+      auto issue_scores = [&](uint32_t d_col, uint32_t a_tile, uint32_t b_tile) {
+        const uint32_t a_lo = desc_lo(a_tile, 16), b_lo = desc_lo(b_tile, 16);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t o = ((kk / 4) * L::kBox + (kk % 4) * 32) >> 4;
+          umma_ss2_w(tmem + d_col, a_lo + o, kDescHi, b_lo + o, kDescHi, kIdescScore, kk > 0);
+        }
+      };
+      // A = packed 16-bit values the elementwise warps left in tensor memory: q columns
+      // 0-63 packed into columns 0-31 of the region, q columns 64-127 into columns 64-95
+      // (each warpgroup packs into its own half).  B = a [128 q, 128 d] tile read MN-major.
+      auto issue_acc = [&](uint32_t d_col, uint32_t a_col, uint32_t b_tile, bool first) {
+        const uint32_t b_lo = desc_lo(b_tile, L::kBox);
+#pragma unroll
+        for (int kk = 0; kk < 128 / 16; ++kk)
+          umma_ts2_w(tmem + d_col, tmem + a_col + (kk >> 2) * 64 + (kk & 3) * 8, b_lo + ((kk * 2048) >> 4), kDescHi,
+                     kIdescAcc, (!first || kk > 0) ? 1u : 0u);
+      };
+      // dQ^T[d, q] = sum_kv K[kv, d] dS^T[kv, q]: both operands read MN-major.
+      auto issue_dq = [&]() {
+        const uint32_t k_lo = desc_lo(k_u32, L::kBox), ds_lo = desc_lo(ds_u32, L::kBox);
+#pragma unroll
+        for (int kk = 0; kk < kRows / 16; ++kk)
+          umma_ss2_w(tmem + L::kColDp, k_lo + ((kk * 2048) >> 4), kDescHi, ds_lo + ((kk * 2048) >> 4), kDescHi, kIdescDq,
+                     kk > 0);
+      };
+      bool ok = warp_wait(SPLASH_WBAR(kv_full, 0), 0, ctx, kWSiteMmaKV, 0) &&
+                warp_wait(SPLASH_WBAR(q_full, 0), 0, ctx, kWSiteMmaQ, 0);
+      if (ok) {
+        tc_fence_after();
+        issue_scores(L::kColS, k_u32, q_u32);
+        umma_commit_w(SPLASH_WBAR(s_ready, 0));
+        ok = warp_wait(SPLASH_WBAR(do_full, 0), 0, ctx, kWSiteMmaDo, 0);
+      }
+      if (ok) {
+        tc_fence_after();
+        issue_scores(L::kColDp, v_u32, do_u32);
+        umma_commit_w(SPLASH_WBAR(dp_ready, 0));
+        for (int t = 0; t < total; ++t) {
+          const int slot = t & 1, nslot = slot ^ 1;
+          const uint32_t par = t & 1;
+          if (!warp_wait(SPLASH_WBAR(p_ready, 0), par, ctx, kWSiteMmaP, t)) break;
+          tc_fence_after();
+          issue_acc(L::kColDv, L::kColS, do_u32, t == 0);                      // dV += P^T dO
+          umma_commit_w(SPLASH_WBAR(do_empty, 0));
+          if (t + 1 < total) {
+            if (!warp_wait(SPLASH_WBAR(q_full, nslot), ((t + 1) >> 1) & 1, ctx, kWSiteMmaQ, t + 1)) break;
+            tc_fence_after();
+            issue_scores(L::kColS, k_u32, q_u32 + nslot * L::kTile);         // S^T(t+1) over P^T(t)
+            umma_commit_w(SPLASH_WBAR(s_ready, 0));
+          }
+          if (!warp_wait(SPLASH_WBAR(ds_ready, 0), par, ctx, kWSiteMmaDs, t)) break;
+          tc_fence_after();
+          issue_acc(L::kColDk, L::kColDp, q_u32 + slot * L::kTile, t == 0);   // dK += dS^T Q
+          umma_commit_w(SPLASH_WBAR(q_empty, slot));
+          issue_dq();                                                          // dQ^T(t) over dS^T(t)
+          umma_commit_w(SPLASH_WBAR(dq_ready, 0));
+          if (t + 1 < total && !warp_wait(SPLASH_WBAR(do_full, 0), par ^ 1, ctx, kWSiteMmaDo, t + 1)) break;
+          // The writer must have taken dQ^T(t) out of R2 (every phase of dq_free is observed).
+          if (!warp_wait(SPLASH_WBAR(dq_free, 0), par, ctx, kWSiteMmaDqFree, t)) break;
+          if (t + 1 < total) {
+            tc_fence_after();
+            issue_scores(L::kColDp, v_u32, do_u32);                            // dP^T(t+1)
+            umma_commit_w(SPLASH_WBAR(dp_ready, 0));
+          }
+        }
+        umma_commit_w(SPLASH_WBAR(acc_done, 0));
+      }
+    }
+  } else if (warp >= kWriterWarp0) {
+    // ================================ dQ writer ==================================
+    setmaxnreg_inc<L::kWriterRegs>();
+    const int wq = warp & 3;
+    const int drow = wq * 32 + lane;  // head-dim index = TMEM lane
+    const uint32_t dq_tmem = tmem + (static_cast<uint32_t>(wq * 32) << 16) + L::kColDp;
+    const bool leader = (warp == kWriterWarp0 && lane == 0);
+    bool alive = true;
+    int t = 0;
+    for (; it.valid() && alive; it.next(), ++t) {
+      const int qblk = a.block_list[it.off()];
+      if (!warp_wait(SPLASH_WBAR(dq_ready, 0), t & 1, ctx, kWSiteWrReady, t)) break;
+      tc_fence_after();
+      uint32_t acc[128];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(dq_tmem + c * 32, acc + c * 32);
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(SPLASH_WBAR(dq_free, 0));
+      const int x = qblk * 128;
+      const int y = (b * a.heads + it.head()) * D;
+      // Four passes of 32 q columns through two 16 KB staging tiles (128 rows of 128 bytes).
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t par = (4 * t + j) & 1;
+        const uint32_t stage = dqs_u32 + (j & 1) * 16384;
+        // The reduction issued from this tile two passes ago must have read it.
+        if ((j >= 2 || t > 0) && leader) bulk_wait_group_read<1>();
+        mbar_arrive(SPLASH_WBAR(wr_a, 0));
+        if (!warp_wait(SPLASH_WBAR(wr_a, 0), par, ctx, kWSiteWrBarA, t)) { alive = false; break; }
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          sts128(stage + swz128(drow, c), make_uint4(acc[j * 32 + c * 4], acc[j * 32 + c * 4 + 1],
+                                                     acc[j * 32 + c * 4 + 2], acc[j * 32 + c * 4 + 3]));
+        fence_proxy_async_smem();
+        mbar_arrive(SPLASH_WBAR(wr_b, 0));
+        if (!warp_wait(SPLASH_WBAR(wr_b, 0), par, ctx, kWSiteWrBarB, t)) { alive = false; break; }
+        if (leader) {
+          tma_reduce_add_2d(&tm_dqacc, stage, x + j * 32, y);
+          bulk_commit_group();
+        }
+      }
+    }
+    if (leader) bulk_wait_group_read<0>();
+  } else {
+    // ========================== elementwise warpgroups ===========================
+    setmaxnreg_inc<L::kEwRegs>();
+    const int w = warp >> 2;                 // which half of the 128 q columns
+    const int wq = warp & 3;
+    const int row = wq * 32 + lane;          // kv row inside the block
+    const int kv_pos = kj * kRows + row;
+    const uint32_t tmem_row = tmem + (static_cast<uint32_t>(wq * 32) << 16);
+    const int col0 = w * 64;                 // first q column this thread handles
+
+    if (total == 0) {
+      // No q block sees this KV block: its gradients are zero.
+      uint8_t* base = static_cast<uint8_t*>(w == 0 ? a.dk : a.dv);
+      uint4* dst = reinterpret_cast<uint4*>(base + static_cast<size_t>(kv_row0 + row) * (D * 2));
+#pragma unroll
+      for (int c = 0; c < D * 2 / 16; ++c) dst[c] = make_uint4(0, 0, 0, 0);
+    } else {
+      const int my_seg = has_seg ? a.seg_kv[static_cast<size_t>(b) * a.kv_len + kv_pos] : 0;
+      const bool cap_on = soft_cap > 0.f;
+      const float cap = soft_cap, inv_cap = cap_on ? 1.f / soft_cap : 0.f;
+      bool alive = true;
+      int cur_mh = -1;
+      int band_lo = -(1 << 30), band_hi = (1 << 30);  // allowed range of kv_pos - q_pos for this kv row
+
+      for (int t = 0; it.valid(); it.next(), ++t) {
+        const int slot = t & 1;
+        const uint32_t par = t & 1;
+        const int off = it.off();
+        const int qblk = a.block_list[off];
+        const bool partial = a.block_kind[off] == SPLASH_BLOCK_PARTIAL;
+        if (a.mask_desc && it.mask_head(it.g) != cur_mh) {
+          cur_mh = it.mask_head(it.g);
+          band_lo = a.mask_desc[cur_mh * 4 + 0];
+          band_hi = a.mask_desc[cur_mh * 4 + 1];
+          const int chunk = a.mask_desc[cur_mh * 4 + 2];
+          if (chunk > 0) {
+            // q must share the kv row's chunk: start <= q_pos <= start + chunk - 1.
+            const int start = (kv_pos / chunk) * chunk;
+            band_lo = max(band_lo, kv_pos - (start + chunk - 1));
+            band_hi = min(band_hi, kv_pos - start);
+          }
+        }
+        const int q0 = qblk * 128 + col0;  // sequence position of this thread's first column
+        // Visibility of this thread's 64 columns (bit i of word c: column c * 32 + i).
+        uint32_t vis[2] = {0xffffffffu, 0xffffffffu};
+        const bool plain_step = !partial && !has_seg && !cap_on;
+        if (!plain_step) {
+          if (partial) {
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+              const int d0 = kv_pos - (q0 + c * 32);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const int d = d0 - i;
+                if (d < band_lo || d > band_hi) vis[c] &= ~(1u << i);
+              }
+            }
+          }
+          if (has_seg) {
+            const int4* sq = reinterpret_cast<const int4*>(a.seg_q + static_cast<size_t>(b) * a.q_len + q0);
+#pragma unroll
+            for (int g = 0; g < 16; ++g) {
+              const int4 sg = __ldg(sq + g);
+              const int c = g >> 3, i = (g & 7) * 4;
+              if (sg.x != my_seg) vis[c] &= ~(1u << (i + 0));
+              if (sg.y != my_seg) vis[c] &= ~(1u << (i + 1));
+              if (sg.z != my_seg) vis[c] &= ~(1u << (i + 2));
+              if (sg.w != my_seg) vis[c] &= ~(1u << (i + 3));
+            }
+          }
+        }
+        if (!warp_wait(SPLASH_WBAR(q_full, slot), (t >> 1) & 1, ctx, kWSiteEwQ, t)) { alive = false; break; }
+        if (!warp_wait(SPLASH_WBAR(s_ready, 0), par, ctx, kWSiteEwS, t)) { alive = false; break; }
+        tc_fence_after();
+
+        // ---- phase A: P^T from S^T; the factor that dS^T needs stays in registers ----
+        float pf[64];
+        {
+          uint32_t* sraw = reinterpret_cast<uint32_t*>(pf);
+          tmem_ld32(tmem_row + L::kColS + col0, sraw);
+          tmem_ld32(tmem_row + L::kColS + col0 + 32, sraw + 32);
+          tmem_wait_ld();
+          uint32_t ppk[32];
+          const uint32_t vec = lse_u32 + slot * L::kVecBytes + col0 * 4;
+          if (plain_step) {
+            // FULL block, no segment ids, no soft-cap: nothing to mask.  (A row whose lse
+            // is mask_value never meets a FULL block, so no guard is needed here.)
+#pragma unroll
+            for (int g = 0; g < 16; ++g) {
+              const uint4 lw = lds128(vec + g * 16);
+              const float nl0 = __uint_as_float(lw.x) * -kLog2e, nl1 = __uint_as_float(lw.y) * -kLog2e;
+              const float nl2 = __uint_as_float(lw.z) * -kLog2e, nl3 = __uint_as_float(lw.w) * -kLog2e;
+              pf[g * 4 + 0] = ex2_approx(fmaf(pf[g * 4 + 0], kLog2e, nl0));
+              pf[g * 4 + 1] = ex2_approx(fmaf(pf[g * 4 + 1], kLog2e, nl1));
+              pf[g * 4 + 2] = ex2_approx(fmaf(pf[g * 4 + 2], kLog2e, nl2));
+              pf[g * 4 + 3] = ex2_approx(fmaf(pf[g * 4 + 3], kLog2e, nl3));
+              ppk[g * 2] = pack2<BF16>(pf[g * 4 + 0], pf[g * 4 + 1]);
+              ppk[g * 2 + 1] = pack2<BF16>(pf[g * 4 + 2], pf[g * 4 + 3]);
+            }
+          } else {
+#pragma unroll
+            for (int g = 0; g < 16; ++g) {
+              const uint4 lw = lds128(vec + g * 16);
+              const float lses[4] = {__uint_as_float(lw.x), __uint_as_float(lw.y), __uint_as_float(lw.z),
+                                     __uint_as_float(lw.w)};
+              float pv[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int i = g * 4 + e;
+                float sval = pf[i];
+                float keep = 1.f;
+                if (cap_on) {
+                  const float th = tanh_approx(sval * inv_cap);
+                  sval = cap * th;
+                  keep = 1.f - th * th;
+                }
+                // Rows that saw no key carry lse = mask_value; they contribute nothing.
+                const bool on = ((vis[i >> 5] >> (i & 31)) & 1u) && lses[e] != a.mask_value;
+                const float p = on ? ex2_approx((sval - lses[e]) * kLog2e) : 0.f;
+                pv[e] = p;
+                pf[i] = p * keep;
+              }
+              ppk[g * 2] = pack2<BF16>(pv[0], pv[1]);
+              ppk[g * 2 + 1] = pack2<BF16>(pv[2], pv[3]);
+            }
+          }
+          // Packed P^T goes over the first half of the columns this thread just read.
+          tmem_st32(tmem_row + L::kColS + col0, ppk);
+          tmem_wait_st();
+          tc_fence_before();
+          mbar_arrive(SPLASH_WBAR(p_ready, 0));
+        }
+
+        // ---- phase B: dS^T from dP^T ---------------------------------------------------
+        if (!warp_wait(SPLASH_WBAR(dp_ready, 0), par, ctx, kWSiteEwDp, t)) { alive = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t dpraw[32];
+          tmem_ld32(tmem_row + L::kColDp + col0 + c * 32, dpraw);
+          tmem_wait_ld();
+          uint32_t dspk[16];
+          const uint32_t vec = delta_u32 + slot * L::kVecBytes + (col0 + c * 32) * 4;
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            const uint4 dw = lds128(vec + g * 16);
+            const int i = c * 32 + g * 4;
+            dspk[g * 2] = pack2<BF16>(pf[i + 0] * (__uint_as_float(dpraw[g * 4 + 0]) - __uint_as_float(dw.x)),
+                                      pf[i + 1] * (__uint_as_float(dpraw[g * 4 + 1]) - __uint_as_float(dw.y)));
+            dspk[g * 2 + 1] = pack2<BF16>(pf[i + 2] * (__uint_as_float(dpraw[g * 4 + 2]) - __uint_as_float(dw.z)),
+                                          pf[i + 3] * (__uint_as_float(dpraw[g * 4 + 3]) - __uint_as_float(dw.w)));
+          }
+          tmem_st16(tmem_row + L::kColDp + col0 + c * 16, dspk);
+          // dS^T staged as [kv row][q], two boxes of 64 q columns, 128-byte swizzle.
+#pragma unroll
+          for (int g = 0; g < 4; ++g)
+            sts128(ds_u32 + w * L::kBox + swz128(row, c * 4 + g),
+                   make_uint4(dspk[g * 4], dspk[g * 4 + 1], dspk[g * 4 + 2], dspk[g * 4 + 3]));
+        }
+        // The slot's vectors have been read.
+        __syncwarp();
+        if (lane == 0) mbar_arrive(SPLASH_WBAR(q_empty, slot));
+        tmem_wait_st();
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(SPLASH_WBAR(ds_ready, 0));
+      }
+
+      // ---- epilogue: dK by warpgroup 0, dV by warpgroup 1 ---------------------------
+      if (alive) alive = warp_wait(SPLASH_WBAR(acc_done, 0), 0, ctx, kWSiteEwDone, total);
+      if (alive) {
+        tc_fence_after();
+        const uint32_t stage = w == 0 ? k_u32 : v_u32;  // K / V tiles are dead once every MMA has finished
+        const uint32_t acc_tmem = tmem_row + (w == 0 ? L::kColDk : L::kColDv);
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld32(acc_tmem + c * 32, o);
+          tmem_wait_ld();
+          const uint32_t box = stage + (c / 2) * L::kBox;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 wv;
+            wv.x = pack2<BF16>(__uint_as_float(o[g * 8 + 0]), __uint_as_float(o[g * 8 + 1]));
+            wv.y = pack2<BF16>(__uint_as_float(o[g * 8 + 2]), __uint_as_float(o[g * 8 + 3]));
+            wv.z = pack2<BF16>(__uint_as_float(o[g * 8 + 4]), __uint_as_float(o[g * 8 + 5]));
+            wv.w = pack2<BF16>(__uint_as_float(o[g * 8 + 6]), __uint_as_float(o[g * 8 + 7]));
+            sts128(box + swz128(row, (c & 1) * 4 + g), wv);
+          }
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(SPLASH_WBAR(epi, w));
+        if (row == 0) {
+          if (mbar_wait(SPLASH_WBAR(epi, w), 0, ctx, kWSiteEwEpi, total)) {
+#pragma unroll
+            for (int c = 0; c < D / 64; ++c) tma_store_2d(w == 0 ? &tm_dk : &tm_dv, stage + c * L::kBox, c * 64, kv_row0);
+            bulk_commit_group();
+            bulk_wait_group_read<0>();
+          }
+        }
+      }
+    }
+  }
+
+  // ---- teardown ---------------------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (const uint32_t gave_up = lds32(abort_u32)) {
+    if (threadIdx.x == 0) report_abort(a.status, gave_up);
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000) {}
+  }
+  if (warp == kProducerWarp0 + 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem, L::kTmemCols);
+  }
+}
+
+#undef SPLASH_WBAR
+
+}  // namespace splash

@@ -24,6 +24,10 @@ int launch_bwd_row(const SplashParams& p, cudaStream_t stream);
 template <int D, int DV, int BC>
 size_t bwd_row_smem(const SplashParams& p);
 
+// Fused backward with 128 q rows per step (head_dim 128, no streamed mask blocks).
+bool bwd_wide_supported(const SplashParams& p);
+int launch_bwd_wide(const SplashParams& p, cudaStream_t stream);
+
 // delta = rowsum(dO * O); dq = cast(transpose(dq_acc)).
 // When `zero` is non-null the same pass also clears zero_floats_per_row floats per row of it.
 int launch_delta(const void* o, const void* d_out, float* delta, long long rows, int head_dim_v, int dtype,
