@@ -24,9 +24,9 @@ static int launch_bwd_wide_typed(const SplashParams& p, cudaStream_t stream) {
   if ((rc = make_tmap_2d(&tm_v, p.v, dt, 2, kv_rows, 128, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if ((rc = make_tmap_2d(&tm_dk, p.dk, dt, 2, kv_rows, 128, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if ((rc = make_tmap_2d(&tm_dv, p.dv, dt, 2, kv_rows, 128, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
-  // f32 accumulator viewed as [batch * heads * head_dim, q_len]; tiles of 32 q columns.
+  // f32 accumulator viewed as [batch * heads * head_dim, q_len]; tiles of 32 rows x 32 q columns.
   const uint64_t acc_rows = static_cast<uint64_t>(p.batch) * p.heads * 128;
-  if ((rc = make_tmap_2d(&tm_dqacc, p.dq_acc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, acc_rows, p.q_len, 128, 32,
+  if ((rc = make_tmap_2d(&tm_dqacc, p.dq_acc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, acc_rows, p.q_len, 32, 32,
                          CU_TENSOR_MAP_SWIZZLE_128B)))
     return rc;
   BwdArgs a;

@@ -39,15 +39,23 @@
 
 #include <stddef.h>
 
+#include <type_traits>
+
 #include "bwd_col_kernel.cuh"  // BwdArgs, ColSteps, math constants
 #include "ptx.cuh"
+
+// Timeline marks for debugging builds; empty in the product.
+#ifndef SPLASH_TRACE_MARK
+#define SPLASH_TRACE_MARK(role, t, k)
+#define SPLASH_TRACE_NS(role, t, k)
+#endif
 
 namespace splash {
 
 enum WideSite : int {
   kWSiteQEmpty = 61, kWSiteDoEmpty, kWSiteMmaKV, kWSiteMmaQ, kWSiteMmaDo, kWSiteMmaP, kWSiteMmaDs, kWSiteMmaDqFree,
   kWSiteEwQ, kWSiteEwS, kWSiteEwDp, kWSiteEwStage, kWSiteEwDone, kWSiteEwEpi,
-  kWSiteWrReady, kWSiteWrBarA, kWSiteWrBarB,
+  kWSiteWrReady,
 };
 
 struct WideLayout {
@@ -60,7 +68,9 @@ struct WideLayout {
   static constexpr int kVecBytes = BC * 4;
   // Shared memory map (bytes from the 1024-aligned base).
   static constexpr int kOffK = 0, kOffV = kTile, kOffQ = 2 * kTile, kOffDo = 4 * kTile, kOffDs = 5 * kTile;
-  static constexpr int kOffDqStage = 6 * kTile;  // two f32 tiles of [128 d, 32 q]
+  static constexpr int kOffDqStage = 6 * kTile;  // per writer warp: kDqBufs f32 tiles of [32 d, 32 q]
+  static constexpr int kDqBufs = 2;
+  static constexpr int kDqBoxBytes = 32 * 32 * 4;
   static constexpr int kOffLse = 7 * kTile, kOffDelta = kOffLse + kSlots * kVecBytes;
   static constexpr int kOffBars = kOffDelta + kSlots * kVecBytes;
   static constexpr int kBarBytes = 256;
@@ -78,7 +88,7 @@ struct WideBarriers {
   uint64_t kv_full;
   uint64_t q_full[2], q_empty[2], do_full, do_empty;
   uint64_t s_ready, dp_ready, p_ready, ds_ready;
-  uint64_t dq_ready, dq_free, wr_a, wr_b;
+  uint64_t dq_ready, dq_free;
   uint64_t acc_done, epi[2];
   uint32_t tmem_base;
   uint32_t abort_flag;
@@ -150,9 +160,7 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       uint32_t count = 1;
       if (off >= offsetof(WideBarriers, q_empty) && off < offsetof(WideBarriers, do_full)) count = 1 + kEwWarps;  // dK + vector readers
       if (off == offsetof(WideBarriers, p_ready) || off == offsetof(WideBarriers, ds_ready)) count = L::kEwThreads;
-      if (off == offsetof(WideBarriers, dq_free) || off == offsetof(WideBarriers, wr_a) ||
-          off == offsetof(WideBarriers, wr_b) || off >= offsetof(WideBarriers, epi))
-        count = 128;
+      if (off == offsetof(WideBarriers, dq_free) || off >= offsetof(WideBarriers, epi)) count = 128;
       mbar_init(bars_u32 + off, count);
     }
     if (lane == 0) {
@@ -278,25 +286,33 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         for (int t = 0; t < total; ++t) {
           const int slot = t & 1, nslot = slot ^ 1;
           const uint32_t par = t & 1;
+          SPLASH_TRACE_MARK(0, t, 0);
           if (!warp_wait(SPLASH_WBAR(p_ready, 0), par, ctx, kWSiteMmaP, t)) break;
+          SPLASH_TRACE_MARK(0, t, 1);
           tc_fence_after();
           issue_acc(L::kColDv, L::kColS, do_u32, t == 0);                      // dV += P^T dO
           umma_commit_w(SPLASH_WBAR(do_empty, 0));
           if (t + 1 < total) {
             if (!warp_wait(SPLASH_WBAR(q_full, nslot), ((t + 1) >> 1) & 1, ctx, kWSiteMmaQ, t + 1)) break;
+            SPLASH_TRACE_MARK(0, t, 2);
             tc_fence_after();
             issue_scores(L::kColS, k_u32, q_u32 + nslot * L::kTile);         // S^T(t+1) over P^T(t)
             umma_commit_w(SPLASH_WBAR(s_ready, 0));
           }
+          SPLASH_TRACE_MARK(0, t, 3);
           if (!warp_wait(SPLASH_WBAR(ds_ready, 0), par, ctx, kWSiteMmaDs, t)) break;
+          SPLASH_TRACE_MARK(0, t, 4);
           tc_fence_after();
           issue_acc(L::kColDk, L::kColDp, q_u32 + slot * L::kTile, t == 0);   // dK += dS^T Q
           umma_commit_w(SPLASH_WBAR(q_empty, slot));
           issue_dq();                                                          // dQ^T(t) over dS^T(t)
           umma_commit_w(SPLASH_WBAR(dq_ready, 0));
+          SPLASH_TRACE_MARK(0, t, 5);
           if (t + 1 < total && !warp_wait(SPLASH_WBAR(do_full, 0), par ^ 1, ctx, kWSiteMmaDo, t + 1)) break;
+          SPLASH_TRACE_MARK(0, t, 6);
           // The writer must have taken dQ^T(t) out of R2 (every phase of dq_free is observed).
           if (!warp_wait(SPLASH_WBAR(dq_free, 0), par, ctx, kWSiteMmaDqFree, t)) break;
+          SPLASH_TRACE_MARK(0, t, 7);
           if (t + 1 < total) {
             tc_fence_after();
             issue_scores(L::kColDp, v_u32, do_u32);                            // dP^T(t+1)
@@ -309,15 +325,17 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   } else if (warp >= kWriterWarp0) {
     // ================================ dQ writer ==================================
     setmaxnreg_inc<L::kWriterRegs>();
+    // Each warp drains its own 32 head-dim rows (its quarter of the TMEM lanes) through
+    // staging tiles of its own, so the writer warps never wait for one another.
     const int wq = warp & 3;
-    const int drow = wq * 32 + lane;  // head-dim index = TMEM lane
     const uint32_t dq_tmem = tmem + (static_cast<uint32_t>(wq * 32) << 16) + L::kColDp;
-    const bool leader = (warp == kWriterWarp0 && lane == 0);
-    bool alive = true;
+    const uint32_t my_stage = dqs_u32 + wq * (L::kDqBufs * L::kDqBoxBytes);
     int t = 0;
-    for (; it.valid() && alive; it.next(), ++t) {
+    for (; it.valid(); it.next(), ++t) {
       const int qblk = a.block_list[it.off()];
+      SPLASH_TRACE_MARK(2, t, 0);
       if (!warp_wait(SPLASH_WBAR(dq_ready, 0), t & 1, ctx, kWSiteWrReady, t)) break;
+      SPLASH_TRACE_MARK(2, t, 1);
       tc_fence_after();
       uint32_t acc[128];
 #pragma unroll
@@ -325,31 +343,30 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       tmem_wait_ld();
       tc_fence_before();
       mbar_arrive(SPLASH_WBAR(dq_free, 0));
+      SPLASH_TRACE_MARK(2, t, 2);
       const int x = qblk * 128;
-      const int y = (b * a.heads + it.head()) * D;
-      // Four passes of 32 q columns through two 16 KB staging tiles (128 rows of 128 bytes).
+      const int y = (b * a.heads + it.head()) * D + wq * 32;
+      // Four passes of 32 q columns: [32 d, 32 q] f32 tiles, 128-byte rows, 128-byte swizzle.
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const uint32_t par = (4 * t + j) & 1;
-        const uint32_t stage = dqs_u32 + (j & 1) * 16384;
-        // The reduction issued from this tile two passes ago must have read it.
-        if ((j >= 2 || t > 0) && leader) bulk_wait_group_read<1>();
-        mbar_arrive(SPLASH_WBAR(wr_a, 0));
-        if (!warp_wait(SPLASH_WBAR(wr_a, 0), par, ctx, kWSiteWrBarA, t)) { alive = false; break; }
+        const uint32_t stage = my_stage + (j % L::kDqBufs) * L::kDqBoxBytes;
+        // The reduction that last used this tile must have read it.
+        if (lane == 0 && (t > 0 || j >= L::kDqBufs)) bulk_wait_group_read<L::kDqBufs - 1>();
+        __syncwarp();
 #pragma unroll
         for (int c = 0; c < 8; ++c)
-          sts128(stage + swz128(drow, c), make_uint4(acc[j * 32 + c * 4], acc[j * 32 + c * 4 + 1],
+          sts128(stage + swz128(lane, c), make_uint4(acc[j * 32 + c * 4], acc[j * 32 + c * 4 + 1],
                                                      acc[j * 32 + c * 4 + 2], acc[j * 32 + c * 4 + 3]));
         fence_proxy_async_smem();
-        mbar_arrive(SPLASH_WBAR(wr_b, 0));
-        if (!warp_wait(SPLASH_WBAR(wr_b, 0), par, ctx, kWSiteWrBarB, t)) { alive = false; break; }
-        if (leader) {
+        __syncwarp();
+        if (lane == 0) {
           tma_reduce_add_2d(&tm_dqacc, stage, x + j * 32, y);
           bulk_commit_group();
         }
       }
+      SPLASH_TRACE_MARK(2, t, 3);
     }
-    if (leader) bulk_wait_group_read<0>();
+    if (lane == 0) bulk_wait_group_read<0>();
   } else {
     // ========================== elementwise warpgroups ===========================
     setmaxnreg_inc<L::kEwRegs>();
@@ -398,14 +415,12 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         const bool plain_step = !partial && !has_seg && !cap_on;
         if (!plain_step) {
           if (partial) {
+            // Column i of word c is visible iff band_lo <= d0 - i <= band_hi: a run of bits.
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
               const int d0 = kv_pos - (q0 + c * 32);
-#pragma unroll
-              for (int i = 0; i < 32; ++i) {
-                const int d = d0 - i;
-                if (d < band_lo || d > band_hi) vis[c] &= ~(1u << i);
-              }
+              const int first = max(0, d0 - band_hi), last = min(31, d0 - band_lo);
+              vis[c] = first <= last ? ((0xffffffffu >> (31 - last)) & (0xffffffffu << first)) : 0u;
             }
           }
           if (has_seg) {
@@ -421,8 +436,11 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             }
           }
         }
+        SPLASH_TRACE_MARK(1, t, 0);
+        SPLASH_TRACE_NS(1, t, 7);
         if (!warp_wait(SPLASH_WBAR(q_full, slot), (t >> 1) & 1, ctx, kWSiteEwQ, t)) { alive = false; break; }
         if (!warp_wait(SPLASH_WBAR(s_ready, 0), par, ctx, kWSiteEwS, t)) { alive = false; break; }
+        SPLASH_TRACE_MARK(1, t, 1);
         tc_fence_after();
 
         // ---- phase A: P^T from S^T; the factor that dS^T needs stays in registers ----
@@ -434,57 +452,61 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           tmem_wait_ld();
           uint32_t ppk[32];
           const uint32_t vec = lse_u32 + slot * L::kVecBytes + col0 * 4;
-          if (plain_step) {
-            // FULL block, no segment ids, no soft-cap: nothing to mask.  (A row whose lse
-            // is mask_value never meets a FULL block, so no guard is needed here.)
+          // One straight-line body per (soft-cap, masking) combination; the step picks one.
+          // Masked entries and rows that saw no key (lse == mask_value) get an exponent of
+          // -inf, i.e. P = 0.  FULL blocks without segment ids need neither test: a row whose
+          // lse is mask_value never meets a FULL block.
+          auto body = [&](auto cap_c, auto mask_c) {
+            constexpr bool kCap = decltype(cap_c)::value, kMask = decltype(mask_c)::value;
 #pragma unroll
             for (int g = 0; g < 16; ++g) {
               const uint4 lw = lds128(vec + g * 16);
-              const float nl0 = __uint_as_float(lw.x) * -kLog2e, nl1 = __uint_as_float(lw.y) * -kLog2e;
-              const float nl2 = __uint_as_float(lw.z) * -kLog2e, nl3 = __uint_as_float(lw.w) * -kLog2e;
-              pf[g * 4 + 0] = ex2_approx(fmaf(pf[g * 4 + 0], kLog2e, nl0));
-              pf[g * 4 + 1] = ex2_approx(fmaf(pf[g * 4 + 1], kLog2e, nl1));
-              pf[g * 4 + 2] = ex2_approx(fmaf(pf[g * 4 + 2], kLog2e, nl2));
-              pf[g * 4 + 3] = ex2_approx(fmaf(pf[g * 4 + 3], kLog2e, nl3));
-              ppk[g * 2] = pack2<BF16>(pf[g * 4 + 0], pf[g * 4 + 1]);
-              ppk[g * 2 + 1] = pack2<BF16>(pf[g * 4 + 2], pf[g * 4 + 3]);
-            }
-          } else {
-#pragma unroll
-            for (int g = 0; g < 16; ++g) {
-              const uint4 lw = lds128(vec + g * 16);
-              const float lses[4] = {__uint_as_float(lw.x), __uint_as_float(lw.y), __uint_as_float(lw.z),
-                                     __uint_as_float(lw.w)};
+              const uint32_t lraw[4] = {lw.x, lw.y, lw.z, lw.w};
               float pv[4];
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
                 const int i = g * 4 + e;
-                float sval = pf[i];
-                float keep = 1.f;
-                if (cap_on) {
+                const float lse_e = __uint_as_float(lraw[e]);
+                float nl = lse_e * -kLog2e;
+                if constexpr (kMask) {
+                  if (lse_e == a.mask_value) nl = -INFINITY;
+                }
+                float sval = pf[i], keep = 1.f;
+                if constexpr (kCap) {
                   const float th = tanh_approx(sval * inv_cap);
                   sval = cap * th;
-                  keep = 1.f - th * th;
+                  keep = fmaf(-th, th, 1.f);
                 }
-                // Rows that saw no key carry lse = mask_value; they contribute nothing.
-                const bool on = ((vis[i >> 5] >> (i & 31)) & 1u) && lses[e] != a.mask_value;
-                const float p = on ? ex2_approx((sval - lses[e]) * kLog2e) : 0.f;
+                float x = fmaf(sval, kLog2e, nl);
+                if constexpr (kMask) {
+                  if (!((vis[i >> 5] >> (i & 31)) & 1u)) x = -INFINITY;
+                }
+                const float p = ex2_approx(x);
                 pv[e] = p;
-                pf[i] = p * keep;
+                pf[i] = kCap ? p * keep : p;
               }
               ppk[g * 2] = pack2<BF16>(pv[0], pv[1]);
               ppk[g * 2 + 1] = pack2<BF16>(pv[2], pv[3]);
             }
-          }
+          };
+          using T = std::true_type;
+          using F = std::false_type;
+          const bool masked = partial || has_seg;
+          if (!cap_on && !masked) body(F{}, F{});
+          else if (!cap_on) body(F{}, T{});
+          else if (!masked) body(T{}, F{});
+          else body(T{}, T{});
           // Packed P^T goes over the first half of the columns this thread just read.
           tmem_st32(tmem_row + L::kColS + col0, ppk);
           tmem_wait_st();
           tc_fence_before();
           mbar_arrive(SPLASH_WBAR(p_ready, 0));
         }
+        SPLASH_TRACE_MARK(1, t, 2);
 
         // ---- phase B: dS^T from dP^T ---------------------------------------------------
         if (!warp_wait(SPLASH_WBAR(dp_ready, 0), par, ctx, kWSiteEwDp, t)) { alive = false; break; }
+        SPLASH_TRACE_MARK(1, t, 3);
         tc_fence_after();
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
@@ -516,6 +538,7 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         fence_proxy_async_smem();
         tc_fence_before();
         mbar_arrive(SPLASH_WBAR(ds_ready, 0));
+        SPLASH_TRACE_MARK(1, t, 4);
       }
 
       // ---- epilogue: dK by warpgroup 0, dV by warpgroup 1 ---------------------------
