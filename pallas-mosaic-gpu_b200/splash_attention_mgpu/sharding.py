@@ -65,6 +65,23 @@ def run_local(fn, q, k, v, segment_ids=None, *, world: int, rank: int):
   return out, span
 
 
+def run_local_grads(fn, q, k, v, d_out, segment_ids=None, *, world: int, rank: int):
+  """Forward and backward of this rank's units: `fn` as for `run_local`, `d_out` like the
+  forward output.  Returns ((out, dq, dk, dv) in unit-major layout, (lo, hi)); nothing
+  crosses ranks, dK/dV of a unit are complete on the rank that owns it.
+  """
+  ql, kl, vl, seg, span = local_units(q, k, v, segment_ids, world, rank)
+  lo, hi = span
+  dol = to_units(d_out, k, v)[0][lo:hi].contiguous()
+  if ql.shape[0] == 0:
+    empty_out = ql.new_zeros((0,) + tuple(ql.shape[1:3]) + (v.shape[-1],))
+    return (empty_out, torch.zeros_like(ql), torch.zeros_like(kl), torch.zeros_like(vl)), span
+  ql, kl, vl = (x.detach().requires_grad_(True) for x in (ql, kl, vl))
+  out = fn(ql, kl, vl, seg) if seg is not None else fn(ql, kl, vl)
+  out.backward(dol)
+  return (out.detach(), ql.grad, kl.grad, vl.grad), span
+
+
 def gather_units(local_out, span, full_shape, group=None):
   """All-gathers per-rank unit outputs into the full [B, H, S, Dv] tensor (for checking only)."""
   import torch.distributed as dist
