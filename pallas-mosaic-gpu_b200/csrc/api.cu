@@ -82,8 +82,14 @@ static int check_bwd(const SplashParams* p) {
   if (p->q_len % 128 || p->kv_len % 128) return fail(SPLASH_INVALID_ARGUMENT, "Sequence lengths must be multiples of 128");
   if (p->sub_block != 0 && p->sub_block != 64 && p->sub_block != 128)
     return fail(SPLASH_INVALID_ARGUMENT, "sub_block must be 0, 64 or 128");
-  if (p->head_dim != p->head_dim_v || (p->head_dim != 64 && p->head_dim != 128))
-    return fail(SPLASH_UNSUPPORTED, "the backward pass supports head_dim == head_dim_v in {64, 128}");
+  if ((p->head_dim != 64 && p->head_dim != 128) || (p->head_dim_v != 64 && p->head_dim_v != 128))
+    return fail(SPLASH_UNSUPPORTED, "the backward pass supports head dims 64 and 128");
+  return SPLASH_OK;
+}
+
+static int check_bwd_fused(const SplashParams* p) {
+  if (int rc = check_bwd(p)) return rc;
+  if (p->head_dim != p->head_dim_v) return fail(SPLASH_UNSUPPORTED, "the fused backward needs head_dim == head_dim_v");
   return SPLASH_OK;
 }
 
@@ -99,12 +105,17 @@ extern "C" int splash_bwd_dq(const SplashParams* p, void* stream) {
   // The requested sub-block is a preference: 128 keys per step when it fits in shared
   // memory, else 64.
   const bool want128 = p->sub_block != 64;
-  if (p->head_dim == 64) {
-    if (want128 && bwd_row_smem<64, 64, 128>(*p) <= kMaxDynamicSmem) return launch_bwd_row<64, 64, 128>(*p, st);
-    return launch_bwd_row<64, 64, 64>(*p, st);
+#define SPLASH_DQ_CASE(D_, DV_)                                                                                  \
+  if (p->head_dim == D_ && p->head_dim_v == DV_) {                                                               \
+    if (want128 && bwd_row_smem<D_, DV_, 128>(*p) <= kMaxDynamicSmem) return launch_bwd_row<D_, DV_, 128>(*p, st); \
+    return launch_bwd_row<D_, DV_, 64>(*p, st);                                                                  \
   }
-  if (want128 && bwd_row_smem<128, 128, 128>(*p) <= kMaxDynamicSmem) return launch_bwd_row<128, 128, 128>(*p, st);
-  return launch_bwd_row<128, 128, 64>(*p, st);
+  SPLASH_DQ_CASE(64, 64)
+  SPLASH_DQ_CASE(128, 128)
+  SPLASH_DQ_CASE(128, 64)
+  SPLASH_DQ_CASE(64, 128)
+#undef SPLASH_DQ_CASE
+  return fail(SPLASH_UNSUPPORTED, "this (head_dim, head_dim_v) pair is not compiled for the dQ kernel");
 }
 
 extern "C" int splash_bwd_dkv(const SplashParams* p, void* stream) {
@@ -113,8 +124,8 @@ extern "C" int splash_bwd_dkv(const SplashParams* p, void* stream) {
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // The kernel works in steps of 64 q rows with double-buffered scores; `sub_block`
   // is accepted for compatibility and does not change the tiling.
-  if (p->head_dim == 64) return launch_bwd_col<64, false>(*p, st);
-  return launch_bwd_col<128, false>(*p, st);
+  if (p->head_dim == 64) return p->head_dim_v == 64 ? launch_bwd_col<64, 64, false>(*p, st) : launch_bwd_col<64, 128, false>(*p, st);
+  return p->head_dim_v == 128 ? launch_bwd_col<128, 128, false>(*p, st) : launch_bwd_col<128, 64, false>(*p, st);
 }
 
 extern "C" int64_t splash_bwd_fused_workspace_bytes(const SplashParams* p) {
@@ -123,7 +134,7 @@ extern "C" int64_t splash_bwd_fused_workspace_bytes(const SplashParams* p) {
 }
 
 extern "C" int splash_bwd_fused(const SplashParams* p, void* stream) {
-  if (int rc = check_bwd(p)) return rc;
+  if (int rc = check_bwd_fused(p)) return rc;
   if (!p->dq || !p->dk || !p->dv || !p->dq_acc) return fail(SPLASH_INVALID_ARGUMENT, "dq, dk, dv and dq_acc must be non-null");
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -141,7 +152,7 @@ extern "C" int splash_bwd_fused(const SplashParams* p, void* stream) {
   const bool wide_off = wide_env && wide_env[0] == '0';
   int rc;
   if (!wide_off && bwd_wide_supported(*p)) rc = launch_bwd_wide(*p, st);
-  else rc = p->head_dim == 64 ? launch_bwd_col<64, true>(*p, st) : launch_bwd_col<128, true>(*p, st);
+  else rc = p->head_dim == 64 ? launch_bwd_col<64, 64, true>(*p, st) : launch_bwd_col<128, 128, true>(*p, st);
   if (rc) return rc;
   return launch_dq_transpose_cast(p->dq_acc, p->dq, static_cast<long long>(p->batch) * p->heads, p->head_dim, p->q_len,
                                   p->dtype, st);
@@ -176,7 +187,7 @@ static int static_dq_acc_address(float** out) {
 }
 
 extern "C" int splash_bwd_fused_static(const SplashParams* p, void* stream) {
-  if (int rc = check_bwd(p)) return rc;
+  if (int rc = check_bwd_fused(p)) return rc;
   SplashParams q = *p;
   const int64_t need = splash_bwd_fused_workspace_bytes(&q);
   if (need <= 0 || static_cast<uint64_t>(need) > kStaticDqAccBytes) {

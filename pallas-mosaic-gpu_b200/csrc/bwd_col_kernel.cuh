@@ -68,20 +68,21 @@ enum BwdSite : int {
 
 constexpr int kColBC = 64;  // q rows per step
 
-template <int D, bool FUSED>
+template <int D, int DV, bool FUSED>
 struct ColLayout {
+  static_assert(!FUSED || D == DV, "the fused kernel needs head_dim == head_dim_v");
   static constexpr int kRows = 128;  // kv rows per CTA
   static constexpr int BC = kColBC;
   static constexpr int kSub = 128 / BC;
   static constexpr int kKBytes = kRows * D * 2;
-  static constexpr int kVBytes = kRows * D * 2;
+  static constexpr int kVBytes = kRows * DV * 2;
   // FUSED at head_dim 64: dQ^T = K^T dS^T is issued with M = 128 like at head_dim 128, and
   // the second 64 rows of its A operand are a second copy of the K tile, so the upper half
   // of the result repeats the lower half and is simply not stored.  That keeps one
   // accumulator layout and one writer for both head dims at the price of idle MMA rows.
   static constexpr int kKDupBytes = (FUSED && D == 64) ? kRows * 128 : 0;
   static constexpr int kQStage = BC * D * 2;
-  static constexpr int kDoStage = BC * D * 2;
+  static constexpr int kDoStage = BC * DV * 2;
   static constexpr int kVecStage = BC * 4;          // lse, delta, q segment ids: BC words each
   static constexpr int kMaskStage = kRows * BC;     // int8, transposed block slice
   static constexpr int kDsStage = kRows * BC * 2;   // FUSED: dS^T as an MMA operand
@@ -89,7 +90,7 @@ struct ColLayout {
   // Tensor memory columns: two S^T buffers, two dP^T buffers, dK, dV.  P^T lives in the
   // S^T buffer it came from, dS^T in the dP^T buffer, dQ^T reuses the dP^T buffer.
   static constexpr int kColS = 0, kColDp = 2 * BC, kColDk = 4 * BC, kColDv = 4 * BC + D;
-  static constexpr int kTmemUsed = 4 * BC + 2 * D;
+  static constexpr int kTmemUsed = 4 * BC + D + DV;
   static constexpr int kTmemCols = 512;
   static constexpr int kEwThreads = 256;
   static constexpr int kThreads = kEwThreads + (FUSED ? 128 : 0) + 128;
@@ -117,6 +118,7 @@ struct ColBarriers {
   uint64_t epi[2];
   uint32_t tmem_base;
   uint32_t abort_flag;
+  uint32_t dead;
 };
 
 #define SPLASH_CBAR(field, idx) \
@@ -165,14 +167,14 @@ struct ColSteps {
 };
 
 // PLAIN: no soft-cap, no segment ids, no streamed mask blocks -- that code is compiled out.
-template <int D, bool FUSED, bool PLAIN, bool BF16>
-__global__ void __launch_bounds__(ColLayout<D, FUSED>::kThreads, 1)
+template <int D, int DV, bool FUSED, bool PLAIN, bool BF16>
+__global__ void __launch_bounds__(ColLayout<D, DV, FUSED>::kThreads, 1)
 splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
                       const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv,
                       const __grid_constant__ CUtensorMap tm_mask, const __grid_constant__ CUtensorMap tm_dqacc,
                       const BwdArgs a) {
-  using L = ColLayout<D, FUSED>;
+  using L = ColLayout<D, DV, FUSED>;
   constexpr int kRows = 128;
   constexpr int BC = kColBC;
   constexpr int kSub = L::kSub;
@@ -198,6 +200,7 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const uint32_t bars_u32 = (segq_u32 + (has_seg ? stages * L::kVecStage : 0) + 15u) & ~15u;
   const uint32_t abort_u32 = bars_u32 + static_cast<uint32_t>(offsetof(ColBarriers, abort_flag));
   const uint32_t tmem_slot_u32 = bars_u32 + static_cast<uint32_t>(offsetof(ColBarriers, tmem_base));
+  const uint32_t dead_u32 = bars_u32 + static_cast<uint32_t>(offsetof(ColBarriers, dead));
 
   const int warp = uniform_warp_index();
   const int lane = threadIdx.x & 31;
@@ -219,8 +222,8 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 
   // One warp initialises the barriers, a lane each, while the MMA warp allocates tensor
   // memory; one CTA barrier later every role starts.  A launch that finds the status
-  // word already set returns without touching data.
-  const bool dead = a.status[0] != 0;
+  // word already set returns without touching data; one thread reads the word and shares
+  // it, so every role of the CTA takes the same branch.
   if (warp == 0) {
     constexpr uint32_t kNumBarriers = offsetof(ColBarriers, tmem_base) / 8;
     for (uint32_t i = lane; i < kNumBarriers; i += 32) {
@@ -231,7 +234,10 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       if (off >= offsetof(ColBarriers, dq_free) && off < offsetof(ColBarriers, tmem_base)) count = 128;  // dq_free, wr_a, wr_b, epi
       mbar_init(bars_u32 + off, count);
     }
-    if (lane == 0) sts32(abort_u32, 0);
+    if (lane == 0) {
+      sts32(abort_u32, 0);
+      sts32(dead_u32, a.status[0] != 0);
+    }
     fence_mbar_init();
     fence_proxy_async_smem();
   } else if (warp == kProducerWarp0 + 1) {
@@ -243,7 +249,7 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   tc_fence_after();
   const uint32_t tmem = lds32(tmem_slot_u32);
   const WaitCtx ctx{abort_u32};
-  if (dead) {
+  if (lds32(dead_u32)) {
     if (warp == kProducerWarp0 + 1) {
       __syncwarp();
       tmem_dealloc(tmem, L::kTmemCols);
@@ -265,7 +271,7 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           tma_load_2d(k_u32 + c * (kRows * 128), &tm_k, c * 64, kv_row0, SPLASH_CBAR(kv_full, 0));
         if constexpr (L::kKDupBytes > 0) tma_load_2d(k_u32 + L::kKBytes, &tm_k, 0, kv_row0, SPLASH_CBAR(kv_full, 0));
 #pragma unroll
-        for (int c = 0; c < D / 64; ++c)
+        for (int c = 0; c < DV / 64; ++c)
           tma_load_2d(v_u32 + c * (kRows * 128), &tm_v, c * 64, kv_row0, SPLASH_CBAR(kv_full, 0));
       }
       int slot = 0;
@@ -286,7 +292,7 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           for (int c = 0; c < D / 64; ++c)
             tma_load_2d(q_u32 + slot * L::kQStage + c * (BC * 128), &tm_q, c * 64, q_row, bar);
 #pragma unroll
-          for (int c = 0; c < D / 64; ++c)
+          for (int c = 0; c < DV / 64; ++c)
             tma_load_2d(do_u32 + slot * L::kDoStage + c * (BC * 128), &tm_do, c * 64, q_row, bar);
           bulk_load_1d(lse_u32 + slot * L::kVecStage, a.lse + q_row, L::kVecStage, bar);
           bulk_load_1d(delta_u32 + slot * L::kVecStage, a.delta + q_row, L::kVecStage, bar);
@@ -301,7 +307,8 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       // ------------------------------- MMA issuer -------------------------------
       // All lanes run the loop; one elected lane issues each instruction.
       constexpr uint32_t kIdescScore = make_idesc(BF16, 128, BC, false, false);   // K Q^T, V dO^T
-      constexpr uint32_t kIdescAcc = make_idesc(BF16, 128, D, false, true);       // P^T dO, dS^T Q
+      constexpr uint32_t kIdescAcc = make_idesc(BF16, 128, D, false, true);       // dS^T Q
+      constexpr uint32_t kIdescAccV = make_idesc(BF16, 128, DV, false, true);     // P^T dO
       constexpr uint32_t kIdescDq = make_idesc(BF16, 128, BC, true, true);        // K^T dS^T
       auto issue_s = [&](int slot, int buf) {
         const uint32_t k_lo = desc_lo(k_u32, 16), q_lo = desc_lo(q_u32 + slot * L::kQStage, 16);
@@ -313,7 +320,7 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       auto issue_dp = [&](int slot, int buf) {
         const uint32_t v_lo = desc_lo(v_u32, 16), do_lo = desc_lo(do_u32 + slot * L::kDoStage, 16);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)
+        for (int kk = 0; kk < DV / 16; ++kk)
           umma_ss2_w(tmem + L::kColDp + buf * BC, v_lo + (((kk / 4) * (kRows * 128) + (kk % 4) * 32) >> 4), kDescHi,
                      do_lo + (((kk / 4) * (BC * 128) + (kk % 4) * 32) >> 4), kDescHi, kIdescScore, kk > 0);
       };
@@ -368,7 +375,7 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 #pragma unroll
             for (int kk = 0; kk < BC / 16; ++kk)
               umma_ts2_w(tmem + L::kColDv, tmem + L::kColS + buf * BC + (kk >> 1) * 32 + (kk & 1) * 8,
-                         do_lo + ((kk * 2048) >> 4), kDescHi, kIdescAcc, (t > 0 || kk > 0) ? 1u : 0u);
+                         do_lo + ((kk * 2048) >> 4), kDescHi, kIdescAccV, (t > 0 || kk > 0) ? 1u : 0u);
           }
           umma_commit_w(SPLASH_CBAR(empty, c_slot));
           if (t + 2 < total) {
@@ -456,9 +463,9 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 #pragma unroll
         for (int c = 0; c < D * 2 / 16; ++c) dst[c] = make_uint4(0, 0, 0, 0);
       } else {
-        uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(a.dv) + static_cast<size_t>(kv_row0 + row) * (D * 2));
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(a.dv) + static_cast<size_t>(kv_row0 + row) * (DV * 2));
 #pragma unroll
-        for (int c = 0; c < D * 2 / 16; ++c) dst[c] = make_uint4(0, 0, 0, 0);
+        for (int c = 0; c < DV * 2 / 16; ++c) dst[c] = make_uint4(0, 0, 0, 0);
       }
     } else {
       const int my_seg = has_seg ? a.seg_kv[static_cast<size_t>(b) * a.kv_len + kv_pos] : 0;
@@ -611,9 +618,11 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         tc_fence_after();
         const uint32_t stage = w == 0 ? k_u32 : v_u32;  // K / V tiles are dead once every MMA has finished
         const uint32_t acc_tmem = tmem_row + (w == 0 ? L::kColDk : L::kColDv);
-        constexpr int kCols = D;
+        constexpr int kMaxCols = D > DV ? D : DV;
+        const int cols = w == 0 ? D : DV;  // uniform per warpgroup
 #pragma unroll
-        for (int c = 0; c < kCols / 32; ++c) {
+        for (int c = 0; c < kMaxCols / 32; ++c) {
+          if (c * 32 >= cols) break;
           uint32_t o[32];
           tmem_ld32(acc_tmem + c * 32, o);
           tmem_wait_ld();
@@ -633,8 +642,8 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         if (row == 0) {
           if (mbar_wait(SPLASH_CBAR(epi, w), 0, ctx, kBSiteEwEpi, total)) {
 #pragma unroll
-            for (int c = 0; c < kCols / 64; ++c)
-              tma_store_2d(w == 0 ? &tm_dk : &tm_dv, stage + c * (kRows * 128), c * 64, kv_row0);
+            for (int c = 0; c < kMaxCols / 64; ++c)
+              if (c * 64 < cols) tma_store_2d(w == 0 ? &tm_dk : &tm_dv, stage + c * (kRows * 128), c * 64, kv_row0);
             bulk_commit_group();
             bulk_wait_group_read<0>();
           }

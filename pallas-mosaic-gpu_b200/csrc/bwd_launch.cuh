@@ -39,9 +39,9 @@ inline void fill_bwd_args(BwdArgs& a, const SplashParams& p, bool dense, bool se
   a.soft_cap = p.soft_cap;
 }
 
-template <int D, bool FUSED, bool BF16>
+template <int D, int DV, bool FUSED, bool BF16>
 int launch_bwd_col_typed(const SplashParams& p, cudaStream_t stream) {
-  using L = ColLayout<D, FUSED>;
+  using L = ColLayout<D, DV, FUSED>;
   constexpr int BC = kColBC;
   const bool dense = p.partial_blocks != nullptr;
   const bool seg = p.seg_q != nullptr;
@@ -63,11 +63,11 @@ int launch_bwd_col_typed(const SplashParams& p, cudaStream_t stream) {
   memset(&tm_dqacc, 0, sizeof tm_dqacc);
   int rc;
   if ((rc = make_tmap_2d(&tm_q, p.q, dt, 2, q_rows, D, BC, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
-  if ((rc = make_tmap_2d(&tm_do, p.d_out, dt, 2, q_rows, D, BC, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  if ((rc = make_tmap_2d(&tm_do, p.d_out, dt, 2, q_rows, DV, BC, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if ((rc = make_tmap_2d(&tm_k, p.k, dt, 2, kv_rows, D, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
-  if ((rc = make_tmap_2d(&tm_v, p.v, dt, 2, kv_rows, D, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  if ((rc = make_tmap_2d(&tm_v, p.v, dt, 2, kv_rows, DV, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if ((rc = make_tmap_2d(&tm_dk, p.dk, dt, 2, kv_rows, D, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
-  if ((rc = make_tmap_2d(&tm_dv, p.dv, dt, 2, kv_rows, D, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  if ((rc = make_tmap_2d(&tm_dv, p.dv, dt, 2, kv_rows, DV, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if (dense) {
     const uint64_t mrows = static_cast<uint64_t>(p.num_partial_blocks) * 128;
     if ((rc = make_tmap_2d(&tm_mask, p.partial_blocks, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, mrows, 128, 128, BC,
@@ -86,7 +86,7 @@ int launch_bwd_col_typed(const SplashParams& p, cudaStream_t stream) {
   a.stages = stages;
   // The kernel without its soft-cap, segment and streamed-mask code when the call uses none.
   const bool plain = p.soft_cap == 0.f && !seg && !dense;
-  auto kernel = plain ? splash_bwd_col_kernel<D, FUSED, true, BF16> : splash_bwd_col_kernel<D, FUSED, false, BF16>;
+  auto kernel = plain ? splash_bwd_col_kernel<D, DV, FUSED, true, BF16> : splash_bwd_col_kernel<D, DV, FUSED, false, BF16>;
   if ((rc = opt_in_smem(kernel, smem))) return rc;
   const unsigned grid = static_cast<unsigned>(a.kv_blocks) * p.kv_heads * p.batch;
   kernel<<<grid, L::kThreads, smem, stream>>>(tm_q, tm_k, tm_v, tm_do, tm_dk, tm_dv, tm_mask, tm_dqacc, a);
@@ -94,10 +94,10 @@ int launch_bwd_col_typed(const SplashParams& p, cudaStream_t stream) {
   return SPLASH_OK;
 }
 
-template <int D, bool FUSED>
+template <int D, int DV, bool FUSED>
 int launch_bwd_col(const SplashParams& p, cudaStream_t stream) {
-  if (p.dtype == SPLASH_DTYPE_BF16) return launch_bwd_col_typed<D, FUSED, true>(p, stream);
-  return launch_bwd_col_typed<D, FUSED, false>(p, stream);
+  if (p.dtype == SPLASH_DTYPE_BF16) return launch_bwd_col_typed<D, DV, FUSED, true>(p, stream);
+  return launch_bwd_col_typed<D, DV, FUSED, false>(p, stream);
 }
 
 template <int D, int DV, int BC>

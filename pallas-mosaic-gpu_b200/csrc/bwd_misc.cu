@@ -95,8 +95,10 @@ template <bool BF16>
 __global__ void __launch_bounds__(256) dq_transpose_cast_kernel(const float* __restrict__ acc, uint16_t* __restrict__ dq,
                                                                 int head_dim, int q_len) {
   __shared__ float tile[64][65];
-  const long long bh = blockIdx.z;
-  const int d0 = blockIdx.y * 64, q0 = blockIdx.x * 64;
+  // blockIdx.x runs over (batch * heads, q tiles): the z extent of a grid stops at 65535.
+  const int q_tiles = q_len / 64;
+  const long long bh = blockIdx.x / q_tiles;
+  const int d0 = blockIdx.y * 64, q0 = (blockIdx.x % q_tiles) * 64;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const float* src = acc + (bh * head_dim + d0) * static_cast<long long>(q_len) + q0;
 #pragma unroll
@@ -127,7 +129,8 @@ __global__ void __launch_bounds__(256) dq_transpose_cast_kernel(const float* __r
 int launch_dq_transpose_cast(const float* acc, void* dq, long long batch_heads, int head_dim, int q_len, int dtype,
                              cudaStream_t stream) {
   if (!acc || !dq || head_dim % 64 || q_len % 64) return fail(SPLASH_INVALID_ARGUMENT, "bad dq cast arguments");
-  dim3 grid(q_len / 64, head_dim / 64, static_cast<unsigned>(batch_heads));
+  if (batch_heads * (q_len / 64) >= (1ll << 31)) return fail(SPLASH_INVALID_ARGUMENT, "batch * heads * q_len too large");
+  dim3 grid(static_cast<unsigned>(batch_heads * (q_len / 64)), head_dim / 64, 1);
   if (dtype == SPLASH_DTYPE_BF16)
     dq_transpose_cast_kernel<true><<<grid, 256, 0, stream>>>(acc, static_cast<uint16_t*>(dq), head_dim, q_len);
   else

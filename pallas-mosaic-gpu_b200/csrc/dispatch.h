@@ -15,7 +15,7 @@ int launch_fwd(const SplashParams& p, cudaStream_t stream);
 
 namespace splash {
 
-template <int D, bool FUSED>
+template <int D, int DV, bool FUSED>
 int launch_bwd_col(const SplashParams& p, cudaStream_t stream);
 
 template <int D, int DV, int BC>

@@ -128,6 +128,7 @@ struct FwdBarriers {
   uint64_t fin;         // alternating warpgroups: partial row sums posted
   uint32_t tmem_base;
   uint32_t abort_flag;
+  uint32_t dead;
 };
 
 #define SPLASH_BAR(field, idx) \
@@ -160,6 +161,7 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const uint32_t share_u32 = bars_u32 + 1024;  // [row maxima | partial sums of group 0 | of group 1]
   const uint32_t abort_u32 = bars_u32 + static_cast<uint32_t>(offsetof(FwdBarriers, abort_flag));
   const uint32_t tmem_slot_u32 = bars_u32 + static_cast<uint32_t>(offsetof(FwdBarriers, tmem_base));
+  const uint32_t dead_u32 = bars_u32 + static_cast<uint32_t>(offsetof(FwdBarriers, dead));
 
   const int warp = uniform_warp_index();
   const int lane = threadIdx.x & 31;
@@ -179,8 +181,8 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   // ---- set-up -----------------------------------------------------------------
   // One warp initialises the barriers, a lane each, while the MMA warp allocates tensor
   // memory; one CTA barrier later every role starts.  A launch that finds the status
-  // word already set (an earlier kernel gave up a wait) returns without touching data.
-  const bool dead = a.status[0] != 0;
+  // word already set (an earlier kernel gave up a wait) returns without touching data; one
+  // thread reads the word and shares it, so every role of the CTA takes the same branch.
   if (warp == 0) {
     constexpr uint32_t kNumBarriers = offsetof(FwdBarriers, tmem_base) / 8;
     for (uint32_t i = lane; i < kNumBarriers; i += 32) {
@@ -193,7 +195,10 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       if (off == offsetof(FwdBarriers, fin)) count = kTile * AW;
       mbar_init(bars_u32 + off, count);
     }
-    if (lane == 0) sts32(abort_u32, 0);
+    if (lane == 0) {
+      sts32(abort_u32, 0);
+      sts32(dead_u32, a.status[0] != 0);
+    }
     fence_mbar_init();
     fence_proxy_async_smem();
   } else if (warp == kSoftmaxWarps + 1) {
@@ -205,7 +210,7 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   tc_fence_after();
   const uint32_t tmem = lds32(tmem_slot_u32);
   const WaitCtx ctx{abort_u32};
-  if (dead) {
+  if (lds32(dead_u32)) {
     if (warp == kSoftmaxWarps + 1) {
       __syncwarp();
       tmem_dealloc(tmem, L::kTmemCols);

@@ -9,6 +9,10 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <map>
+#include <mutex>
+#include <utility>
+
 #include "../../include/splash_sm100.h"
 
 namespace splash {
@@ -70,10 +74,25 @@ inline CUtensorMapDataType tmap_dtype(int dtype) {
   return dtype == SPLASH_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
 }
 
+// Raises a kernel's dynamic shared-memory limit.  The attribute is per function and device and only
+// ever needs to grow, so the largest size set so far is remembered per (function, device) and later
+// calls cost one map lookup instead of a driver call.
+inline int opt_in_smem_impl(const void* kernel, size_t bytes) {
+  static std::mutex mu;
+  static std::map<std::pair<const void*, int>, int> granted;
+  int dev = 0;
+  SPLASH_CUDA_CHECK(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lock(mu);
+  int& have = granted[std::make_pair(kernel, dev)];
+  if (have >= static_cast<int>(bytes)) return SPLASH_OK;
+  SPLASH_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)));
+  have = static_cast<int>(bytes);
+  return SPLASH_OK;
+}
+
 template <typename Kernel>
 inline int opt_in_smem(Kernel kernel, size_t bytes) {
-  SPLASH_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)));
-  return SPLASH_OK;
+  return opt_in_smem_impl(reinterpret_cast<const void*>(kernel), bytes);
 }
 
 constexpr size_t kMaxDynamicSmem = 227 * 1024;

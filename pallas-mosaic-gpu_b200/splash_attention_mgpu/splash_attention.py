@@ -45,6 +45,7 @@ _TORCH_DTYPES = {torch.bfloat16: _ffi.DTYPE_BF16, torch.float16: _ffi.DTYPE_F16}
 # ---------------------------------------------------------------------------
 
 _status_words: dict = {}
+_status_mirrors: dict = {}   # device key -> (pinned host copy of the word, event recorded after the copy)
 
 
 def _status_word(device: torch.device) -> torch.Tensor:
@@ -53,6 +54,16 @@ def _status_word(device: torch.device) -> torch.Tensor:
   if key not in _status_words:
     _status_words[key] = torch.zeros(4, dtype=torch.int32, device=device)
   return _status_words[key]
+
+
+def _raise_device_status(word: torch.Tensor, host) -> None:
+  """Clears the device word (later launches would return at entry while it is set) and raises."""
+  code, site, block, step = (int(x) for x in host)
+  word.zero_()
+  raise _ffi.SplashLibraryError(
+      f"splash attention kernel: a kernel gave up waiting (code {code} at wait site {site}, block {block},"
+      f" step {step}); outputs of calls since the last check are invalid.  The status word has been"
+      " cleared; the call may be repeated.")
 
 
 def check_device_status(device=None) -> None:
@@ -65,14 +76,42 @@ def check_device_status(device=None) -> None:
     with torch.cuda.device(word.device):
       stream = torch.cuda.current_stream(word.device).cuda_stream
       rc = lib.splash_read_status(word.data_ptr(), ctypes.byref(host), stream)
-    if rc != _ffi.SPLASH_OK:
-      word.zero_()
-      _ffi.check(rc, "splash attention kernel")
+    _status_mirrors.pop(key, None)
+    if rc == _ffi.SPLASH_DEVICE_TIMEOUT:
+      _raise_device_status(word, host)
+    _ffi.check(rc, "splash attention kernel")
+
+
+def _poll_status(device) -> None:
+  """Start of a call: raises if the copy queued by an earlier call has landed and shows a failure.
+  Never waits for the device."""
+  mirror = _status_mirrors.get((device.type, device.index))
+  if mirror is None or torch.cuda.is_current_stream_capturing():
+    return
+  host, event = mirror
+  if event.query() and int(host[0]) != 0:
+    _status_mirrors.pop((device.type, device.index), None)
+    _raise_device_status(_status_word(device), host.tolist())
 
 
 def _maybe_check(device) -> None:
-  if os.environ.get("SPLASH_CHECK_STATUS", "0") == "1":
+  """End of a call.  SPLASH_CHECK_STATUS: "1" synchronises and checks now, "0" checks nothing, anything
+  else (the default) queues a 16-byte copy of the status word to pinned host memory behind the
+  kernels; the next call on this device, or `check_device_status`, looks at it."""
+  mode = os.environ.get("SPLASH_CHECK_STATUS", "async")
+  if mode == "1":
     check_device_status(device)
+    return
+  if mode == "0" or torch.cuda.is_current_stream_capturing():
+    return
+  key = (device.type, device.index)
+  mirror = _status_mirrors.get(key)
+  if mirror is None:
+    mirror = (torch.zeros(4, dtype=torch.int32).pin_memory(), torch.cuda.Event())
+    _status_mirrors[key] = mirror
+  host, event = mirror
+  host.copy_(_status_word(device), non_blocking=True)
+  event.record(torch.cuda.current_stream(device))
 
 
 class _DeviceSchedule(NamedTuple):
@@ -410,6 +449,7 @@ def _forward(kernel: SplashAttentionKernel, bs: BlockSizes, q, k, v,
              segment_ids, *, save_residuals: bool):
   """Runs one forward kernel; returns (out, lse or None)."""
   lib = _ffi.load()
+  _poll_status(q.device)
   sched = kernel._fwd_schedule(bs, q.device)
   _validate_forward(q, k, v, bs, sched, segment_ids, save_residuals)
   q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
@@ -457,6 +497,7 @@ def _backward(kernel: SplashAttentionKernel, bs: BlockSizes, q, k, v,
                "splash_bwd_fused"):
     if not hasattr(lib, name):
       raise _ffi.SplashLibraryError(f"{_ffi.LIB_NAME} does not export {name}")
+  _poll_status(q.device)
   rows, cols = kernel._bwd_schedules(q.device)
   d_out = d_out.to(q.dtype).contiguous()
   batch, heads, q_len, head_dim = q.shape

@@ -4,7 +4,12 @@ CPU oracle's analytic gradients.
 Case lists replay the reference's gradient tiers (tests/test_splash_attention_mgpu.py:
 397-457 split kernels, 563-589 fused head_dim 128, 492-521 ping-pong forward + backward
 and tiling independence) at s = 2048; the bar is the reference's:
-max|g - r| / max|r| < 2e-2 per tensor.
+max|g - r| / max|r| < 2e-2 per tensor.  Those cases draw q unscaled, as the reference's
+tests do, which makes the softmax nearly one-hot; the mean relative error of bf16
+gradients is then 6e-3 to 9e-3 for dQ/dK (P and dS are rounded to 16 bits before the
+products, here as in the reference), so it is bounded at 1e-2 there.  With q pre-scaled by
+head_dim^-0.5 -- the benchmark configurations' convention -- the bar is the tighter one
+those configurations are specified with: mean relative error <= 5e-3 per tensor.
 """
 
 import os
@@ -24,13 +29,13 @@ _id = lambda kw: ",".join(f"{k}={v}" for k, v in kw.items()) or "default"
 
 
 def _check_grads(mask_name, *, s=2048, b=None, h=2, kvh=None, d=64, mqa=False, segs=False, cap=None,
-                 block_sizes=sa.BlockSizes(), multi_head_mask=False, dtype=torch.bfloat16):
+                 block_sizes=sa.BlockSizes(), multi_head_mask=False, dtype=torch.bfloat16, scaled=False, dv=None):
   kvh = kvh or h
   mask, dense = build_mask(mask_name, s, h, multi_head_mask)
   make = sa.make_splash_mqa if mqa else sa.make_splash_mha
   kernel = make(mask, block_sizes=block_sizes, attn_logits_soft_cap=cap)
-  q, k, v = inputs(b, h, kvh, s, d, d, dtype, mqa, device="cuda:0")
-  w = torch.randn(q.shape, generator=torch.Generator().manual_seed(7)).to("cuda:0")
+  q, k, v = inputs(b, h, kvh, s, d, dv or d, dtype, mqa, device="cuda:0", scale=d ** -0.5 if scaled else 1.0)
+  w = torch.randn(q.shape[:-1] + (dv or d,), generator=torch.Generator().manual_seed(7)).to("cuda:0")
   seg = segments(s, "cuda:0") if segs else None
   qg, kg, vg = (x.clone().requires_grad_(True) for x in (q, k, v))
   out = kernel(qg, kg, vg, seg)
@@ -43,7 +48,7 @@ def _check_grads(mask_name, *, s=2048, b=None, h=2, kvh=None, d=64, mqa=False, s
     rel = np.abs(g - r).max() / np.abs(r).max()
     assert rel < 2e-2, f"d{name}: relative error {rel}"
     mean_rel = np.abs(g - r).mean() / np.abs(r).mean()
-    assert mean_rel < 1e-2, f"d{name}: mean relative error {mean_rel}"
+    assert mean_rel <= (5e-3 if scaled else 1e-2), f"d{name}: mean relative error {mean_rel}"
 
 
 GRAD_CASES = [
@@ -95,6 +100,27 @@ GRAD_CASES_D128 = [
 ]
 
 
+GRAD_CASES_SCALED = [
+    dict(mask_name="causal", d=128),
+    dict(mask_name="full", d=128),
+    dict(mask_name="local", d=128, segs=True),
+    dict(mask_name="chunked", d=128, h=4, kvh=2),
+    dict(mask_name="causal", d=128, cap=50.0),
+    dict(mask_name="causal", d=128, dtype=torch.float16),
+    dict(mask_name="dense", d=128),
+    dict(mask_name="causal", d=64),
+    dict(mask_name="local", d=64, segs=True, dtype=torch.float16),
+    dict(mask_name="dense", d=64, h=4, kvh=2),
+]
+
+
+@pytest.mark.parametrize("kwargs", GRAD_CASES_SCALED, ids=_id)
+def test_gpu_grads_prescaled_q_mean_error(kwargs):
+  # q scaled by head_dim^-0.5: max relative error < 2e-2 and mean relative error <= 5e-3.
+  kwargs = dict(kwargs)
+  _check_grads(kwargs.pop("mask_name"), scaled=True, **kwargs)
+
+
 @pytest.mark.parametrize("kwargs", GRAD_CASES_D128, ids=_id)
 def test_gpu_grads_fused(kwargs):
   kwargs = dict(kwargs)
@@ -105,6 +131,24 @@ def test_gpu_grads_fused(kwargs):
 def test_gpu_grads_split_d128(kwargs, monkeypatch):
   # SPLASH_BWD_FUSED=0 routes head_dim 128 through the dQ + dK/dV kernels.
   monkeypatch.setenv("SPLASH_BWD_FUSED", "0")
+  kwargs = dict(kwargs)
+  _check_grads(kwargs.pop("mask_name"), **kwargs)
+
+
+GRAD_CASES_MIXED = [
+    dict(mask_name="causal", d=128, dv=64),
+    dict(mask_name="causal", d=64, dv=128),
+    dict(mask_name="dense", d=128, dv=64, segs=True),
+    dict(mask_name="local", d=64, dv=128, segs=True, h=4, kvh=2),
+    dict(mask_name="chunked", d=128, dv=64, cap=5.0, dtype=torch.float16),
+    dict(mask_name="full", d=64, dv=128, mqa=True, h=3),
+]
+
+
+@pytest.mark.parametrize("kwargs", GRAD_CASES_MIXED, ids=_id)
+def test_gpu_grads_head_dim_v_differs(kwargs):
+  # head_dim != head_dim_v goes through the split dQ and dK/dV kernels
+  # (reference: backward.py:103,116-117,397,417 take head_dim_v from v).
   kwargs = dict(kwargs)
   _check_grads(kwargs.pop("mask_name"), **kwargs)
 

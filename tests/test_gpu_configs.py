@@ -33,13 +33,17 @@ def _check_rows(dense_rows_fn, q, k, v, out, lse, rows, heads, *, seg=None, cap=
     sg = None if seg is None else (seg[0][b, rows].cpu().numpy(), seg[1][b].cpu().numpy())
     ref, ref_lse = oracle.attention_forward(mask_rows, qs, ks[None] if mqa else ks, vs[None] if mqa else vs, sg,
                                             attn_logits_soft_cap=cap)
-    np.testing.assert_allclose(out[b, h, rows].float().cpu().numpy(), ref[0], atol=tol, rtol=tol)
+    got_out = out[b, h, rows].float().cpu().numpy()
+    np.testing.assert_allclose(got_out, ref[0], atol=tol, rtol=tol)
+    assert np.abs(got_out - ref[0]).mean() / np.abs(ref[0]).mean() <= 5e-3, "out: mean relative error"
     np.testing.assert_allclose(lse[b, h, rows].cpu().numpy(), ref_lse[0], atol=1e-3, rtol=1e-3)
     if dq is not None:
       want_dq, _, _ = oracle.attention_backward(mask_rows, qs, ks, vs, d_out[b, h:h + 1, rows], sg,
                                                 attn_logits_soft_cap=cap)
       got = dq[b, h, rows].float().cpu().numpy()
       assert np.abs(got - want_dq[0]).max() / np.abs(want_dq).max() < 2e-2
+      mean_rel = np.abs(got - want_dq[0]).mean() / np.abs(want_dq[0]).mean()
+      assert mean_rel <= 5e-3, f"dq: mean relative error {mean_rel}"
 
 
 def _grads(kernel, q, k, v, d_out, seg=None):
@@ -58,9 +62,11 @@ def _check_unit(dense, q, k, v, d_out, dk, dv, b, kvh, *, seg=None, cap=None):
   mask = dense if dense.shape[0] == 1 else dense[hs]
   _, want_dk, want_dv = oracle.attention_backward(mask, q[b, hs], k[b, kvh:kvh + 1], v[b, kvh:kvh + 1], d_out[b, hs],
                                                   sg, attn_logits_soft_cap=cap)
-  for got, want in ((dk[b, kvh], want_dk[0]), (dv[b, kvh], want_dv[0])):
+  for name, got, want in (("dk", dk[b, kvh], want_dk[0]), ("dv", dv[b, kvh], want_dv[0])):
     got = got.float().cpu().numpy()
     assert np.abs(got - want).max() / np.abs(want).max() < 2e-2
+    mean_rel = np.abs(got - want).mean() / np.abs(want).mean()
+    assert mean_rel <= 5e-3, f"{name}: mean relative error {mean_rel}"
 
 
 def test_causal_b2_h16_s8192_d128_forward_backward():

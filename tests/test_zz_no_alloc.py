@@ -6,7 +6,10 @@ cannot call cudaMalloc and have no scratch to lend.  For them the library carrie
 fixed 16 MiB f32 dQ accumulator of its own.  This test drives that entry point through
 the C ABI twice in a row (the array keeps the previous call's contents, so the second
 call proves it is cleared) and compares dq, dk, dv with the regular entry point, which
-takes caller scratch.  It also checks that an oversized problem is refused.
+takes caller scratch, and with the CPU oracle.  Around the second call it reads the
+driver's free-memory figure, which must not move, and it hands the entry point a bogus
+`dq_acc` pointer, which must be ignored.  It also checks that an oversized problem is
+refused.
 
 The file sorts last on purpose: a run that stops at the first failure has then
 already run every other test.
@@ -19,6 +22,7 @@ import pytest
 import torch
 
 import splash_attention_mgpu as sa
+from oracle import dense_attention as oracle
 from splash_attention_mgpu import _ffi
 from splash_attention_mgpu import splash_attention as impl
 
@@ -67,20 +71,30 @@ def test_static_scratch_matches_caller_scratch_twice():
   _ffi.check(lib.splash_bwd_fused(ctypes.byref(p), stream), "fused")
   torch.cuda.synchronize()
   sa.check_device_status()
+  s = keep["q"].shape[2]
+  ref = oracle.attention_backward(np.tril(np.ones((s, s), bool))[None], keep["q"], keep["k"], keep["v"], keep["do"])
   for attempt in range(2):
     got = _grads_like(keep)
     for t in got:
       t.fill_(float("nan"))
     p = params(*got)
-    p.dq_acc = None  # no scratch from the caller
+    # No scratch from the caller; whatever stands in the field is ignored (second call: a bogus address).
+    p.dq_acc = None if attempt == 0 else 0x10
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
     _ffi.check(lib.splash_bwd_fused_static(ctypes.byref(p), stream), "fused static")
     torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    if attempt == 1:  # the first call on a device may load the kernels' code; the second allocates nothing
+      assert free_after == free_before, f"device free memory moved by {free_before - free_after} bytes"
     sa.check_device_status()
-    for name, a, b in zip(("dq", "dk", "dv"), got, want):
+    for name, a, b, r in zip(("dq", "dk", "dv"), got, want, ref):
       a, b = a.float().cpu().numpy(), b.float().cpu().numpy()
       assert np.isfinite(a).all(), (attempt, name)
       rel = np.abs(a - b).max() / np.abs(b).max()
-      assert rel < 2e-2, f"call {attempt}, {name}: relative difference {rel}"
+      assert rel < 2e-2, f"call {attempt}, {name}: relative difference {rel} to the regular entry point"
+      rel = np.abs(a - r).max() / np.abs(r).max()
+      assert rel < 2e-2, f"call {attempt}, {name}: relative error {rel} against the oracle"
 
 
 def test_static_scratch_refuses_oversized_problems():
