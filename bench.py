@@ -67,6 +67,9 @@ class Workload:
   forward_only: bool = False
   block_q: int | None = None
   block_kv: int | None = None
+  # Granularity at which useful blocks are counted: the 128 x 128 schedule, as the reference does,
+  # unless the mask itself is defined on another grid.
+  count_blocks: tuple = (128, 128)
 
 
 WORKLOADS = {
@@ -76,7 +79,12 @@ WORKLOADS = {
     "packed_full_b4_h16_s8192_d64_f16": Workload("packed_full", 4, 16, 16, 8192, 64, "f16", segments=True),
     "packed_per_head_b4_h16_s8192_d64_f16": Workload("packed_per_head", 4, 16, 16, 8192, 64, "f16", segments=True),
     "mqa_block_sparse_h64_s32768_d256_bf16": Workload("block_sparse", 1, 64, 1, 32768, 256, "bf16", mqa=True,
-                                                      forward_only=True, block_q=128, block_kv=64),
+                                                      forward_only=True, block_q=128, block_kv=64,
+                                                      count_blocks=(128, 64)),
+    # The same mask with 8 q heads: small enough for a profiler capture (a few hundred MB on the device).
+    "mqa_block_sparse_h8_s32768_d256_bf16": Workload("block_sparse", 1, 8, 1, 32768, 256, "bf16", mqa=True,
+                                                     forward_only=True, block_q=128, block_kv=64,
+                                                     count_blocks=(128, 64)),
     # Extra shapes.
     "full_b1_h16_s16384_d128_bf16": Workload("full", 1, 16, 16, 16384, 128, "bf16"),
     "causal_b4_h16_s8192_d64_f16": Workload("causal", 4, 16, 16, 8192, 64, "f16"),
@@ -153,7 +161,7 @@ def packed_segments(batch, seq, seed=7):
 
 def visible_blocks_per_head(sa, wl, masks):
   """Visible schedule blocks of each q head and the FLOPs of one block (reference accounting)."""
-  bq, bkv = (128, 128) if wl.block_kv is None else (wl.block_q or 128, wl.block_kv)
+  bq, bkv = wl.count_blocks
   per_head = []
   for m in (masks if len(masks) > 1 else masks[:1]):
     info = sa.process_mask(m, (bq, bkv))
@@ -426,6 +434,8 @@ def run_ours(args):
   torch.autograd.graph.set_warn_on_accumulate_grad_stream_mismatch(False)
   wl_name = args.workload
   wl = WORKLOADS[wl_name]
+  if args.block_q or args.block_kv:   # tiling override (profiling a particular kernel)
+    wl = dataclasses.replace(wl, block_q=args.block_q or wl.block_q, block_kv=args.block_kv or wl.block_kv)
   dtype = torch_dtype(wl)
   part = Partition(sa, wl, world, rank)
   kernel = part.kernel
@@ -749,6 +759,8 @@ def main():
   p.add_argument("--no-sdpa", action="store_true", help="skip the torch SDPA (cuDNN) comparator")
   p.add_argument("--no-graph", action="store_true", help="time eager calls only")
   p.add_argument("--no-sustained", action="store_true", help="skip the two-second loop")
+  p.add_argument("--block-q", type=int, default=None, help="forward tile rows (128 or 256) instead of the automatic choice")
+  p.add_argument("--block-kv", type=int, default=None, help="forward KV block width (64 or 128)")
   args = p.parse_args()
   if args.impl == "reference":
     run_reference(args)

@@ -10,8 +10,9 @@
  * Conventions
  *   - Plain pointers and sizes only; every buffer is owned by the caller and lives
  *     in device memory unless stated otherwise.  Except where an entry point says
- *     so, the library allocates no device memory and keeps no state besides cached
- *     function attributes.
+ *     so, the library allocates no device memory and keeps no state besides what it
+ *     remembers per device: the shared-memory limit already granted to each kernel
+ *     and (splash_bwd_fused_static) the address of its built-in scratch.
  *   - Calls enqueue work on `stream` (a cudaStream_t passed as void*) and return
  *     without synchronising.
  *   - Return value: SPLASH_OK or a negative SplashStatus.  Nothing is thrown
@@ -60,9 +61,11 @@ typedef struct SplashParams {
   const int32_t* block_list;  /* [mask_heads, blocks, max_steps] visited blocks */
   const int32_t* block_kind;  /* [mask_heads, blocks, max_steps] PARTIAL/FULL   */
   const int32_t* mask_block;  /* [mask_heads, blocks, max_steps] or NULL        */
-  /* Dense partial blocks, int8, 1 = attend: [n, block_q, block_kv] for the row
-   * kernels, [n, block_kv, block_q] (transposed) for the column kernels. NULL
-   * when partial blocks are computed from `mask_desc`. */
+  /* Dense partial blocks, one bit per element (1 = attend), bit i of byte j standing for
+   * column 8 * j + i: [n, block_q, block_kv / 8] bytes for the row kernels,
+   * [n, block_kv, block_q / 8] (transposed) for the column kernels; 16-byte aligned.
+   * NULL when partial blocks are computed from `mask_desc`.  (The reference streams
+   * int8 blocks, splash_attention_mgpu/mask_info.py:113-120.) */
   const int8_t* partial_blocks;
   /* [mask_heads, 4] int32 {lo, hi, chunk, 0}: a key is visible iff
    * lo <= kv_pos - q_pos <= hi and (chunk == 0 or q_pos/chunk == kv_pos/chunk).
@@ -74,7 +77,9 @@ typedef struct SplashParams {
   void* dq;         /* backward: like q                                         */
   void* dk;         /* backward: like k                                         */
   void* dv;         /* backward: like v                                         */
-  float* dq_acc;    /* fused backward scratch: f32 [batch, heads, q_len, head_dim] */
+  float* dq_acc;    /* fused backward scratch: f32, transposed -- [batch, heads, head_dim, q_len],
+                     * i.e. [batch * heads * head_dim, q_len] row-major; size from
+                     * splash_bwd_fused_workspace_bytes()                         */
   int32_t* status;  /* 4 x int32, see above                                     */
   /* ---- static configuration ---------------------------------------------- */
   int32_t batch, heads, kv_heads, q_len, kv_len, head_dim, head_dim_v;
@@ -87,7 +92,21 @@ typedef struct SplashParams {
   int32_t sub_block;          /* backward contraction sub-block (64/128), 0=auto */
   float mask_value;           /* lse reported for rows that see no key           */
   float soft_cap;             /* logits -> cap * tanh(logits / cap); 0 = off     */
+  /* ---- optional scratch (appended; zero/NULL keeps the behaviour without it) ---- */
+  /* Segment-aware block skipping.  With segment ids, int32 scratch of
+   * splash_seg_ranges_bytes() bytes: every entry point that is given it first fills it with
+   * the smallest and largest segment id of every 64 positions of seg_q and seg_kv, and its
+   * CTAs then leave out scheduled blocks whose q and kv id ranges cannot meet, and skip the
+   * per-element comparison in blocks where both sides carry one and the same id.  The
+   * reference computes every scheduled block and masks by comparison
+   * (splash_attention_mgpu/kernel.py:392-395); results are the same.  NULL: as the reference. */
+  int32_t* seg_ranges;
 } SplashParams;
+
+/* Bytes of `seg_ranges` scratch for these shapes (0 when there are no segment ids).  No
+ * counterpart in the reference, which computes every scheduled block and masks by
+ * comparing ids (splash_attention_mgpu/kernel.py:392-395). */
+int64_t splash_seg_ranges_bytes(const SplashParams* p);
 
 /* Forward, one 128-row q tile per CTA.  Replaces the custom call made by
  * `_splash_attention_forward` (reference splash_attention_mgpu/kernel.py:521-537). */
@@ -114,7 +133,8 @@ int splash_bwd_dq(const SplashParams* p, void* stream);
 int splash_bwd_dkv(const SplashParams* p, void* stream);
 
 /* Fused backward (dQ, dK, dV in one kernel; dQ reduce-added into `dq_acc`, which
- * this call zeroes first and converts into `dq` afterwards).  Replaces
+ * this call zeroes first and converts into `dq` afterwards).  head_dim == head_dim_v
+ * in {64, 128}; other pairs of 64/128 go through splash_bwd_dq + splash_bwd_dkv.  Replaces
  * `splash_attention_bwd_fused` together with its accumulator zero-fill and
  * transpose/cast passes (reference splash_attention_mgpu/backward_fused.py:492-511).
  * With `out` null, `delta` must already hold rowsum(dO * O) (splash_bwd_delta); with
@@ -145,7 +165,10 @@ int64_t splash_bwd_fused_workspace_bytes(const SplashParams* p);
  * batch * heads * q_len * head_dim * 4 > SPLASH_STATIC_DQ_ACC_BYTES are refused with
  * SPLASH_BUDGET_EXCEEDED.  The call performs no cudaMalloc / cudaFree and no allocating
  * library call.  The first call on each device looks up the array's device address
- * (cudaGetSymbolAddress); make that first call outside any stream capture.
+ * (cudaGetSymbolAddress); make that first call outside any stream capture.  The address
+ * is remembered per device ordinal for the life of the process and does not survive
+ * cudaDeviceReset or the destruction of the device's primary context: a process that
+ * does either must not call this entry point on that device again.
  *
  * All calls share the one array: it is cleared at the start of each call, and two calls
  * whose GPU work overlaps (different streams, no ordering between them) race on it --
@@ -167,6 +190,9 @@ const char* splash_last_error(void);
  *   a_mode: 0 = A in shared memory, K-major (global A is [128, kd] row-major)
  *           1 = A in shared memory, M-major (global A is [kd, 128] row-major)
  *           2 = A staged through tensor memory (global A is [128, kd] row-major)
+ *           3 = no GEMM: the kernel waits on a barrier nothing arrives on, so that its
+ *               bounded wait runs out (about a second); it then unwinds and leaves
+ *               {1, 102, 0, 7} in `status`.  Checks the report path without a fault.
  *   b_mode: 0 = K-major (global B is [n, kd] row-major)
  *           1 = N-major (global B is [kd, n] row-major)
  * No counterpart in the reference; it exists for the test-suite. */

@@ -54,9 +54,15 @@ static int check_fwd(const SplashParams* p, int tiles) {
 
 using namespace splash;
 
+extern "C" int64_t splash_seg_ranges_bytes(const SplashParams* p) {
+  if (!p || !p->seg_q || p->q_len % 64 || p->kv_len % 64) return 0;
+  return static_cast<int64_t>(p->batch) * (p->q_len / 64 + p->kv_len / 64) * 8;
+}
+
 extern "C" int splash_fwd128(const SplashParams* p, void* stream) {
   if (int rc = check_fwd(p, 1)) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (int rc = launch_seg_ranges(*p, st)) return rc;
   SPLASH_FWD_CASE(64, 64, 1)
   SPLASH_FWD_CASE(64, 128, 1)
   SPLASH_FWD_CASE(128, 128, 1)
@@ -69,6 +75,7 @@ extern "C" int splash_fwd128(const SplashParams* p, void* stream) {
 extern "C" int splash_fwd256(const SplashParams* p, void* stream) {
   if (int rc = check_fwd(p, 2)) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (int rc = launch_seg_ranges(*p, st)) return rc;
   if (p->head_dim != p->head_dim_v) return fail(SPLASH_UNSUPPORTED, "ping-pong kernel needs head_dim == head_dim_v");
   SPLASH_FWD_CASE(64, 64, 2)
   SPLASH_FWD_CASE(128, 128, 2)
@@ -102,6 +109,7 @@ extern "C" int splash_bwd_dq(const SplashParams* p, void* stream) {
   if (int rc = check_bwd(p)) return rc;
   if (!p->dq) return fail(SPLASH_INVALID_ARGUMENT, "dq is null");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (int rc = launch_seg_ranges(*p, st)) return rc;
   // The requested sub-block is a preference: 128 keys per step when it fits in shared
   // memory, else 64.
   const bool want128 = p->sub_block != 64;
@@ -122,6 +130,7 @@ extern "C" int splash_bwd_dkv(const SplashParams* p, void* stream) {
   if (int rc = check_bwd(p)) return rc;
   if (!p->dk || !p->dv) return fail(SPLASH_INVALID_ARGUMENT, "dk / dv is null");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (int rc = launch_seg_ranges(*p, st)) return rc;
   // The kernel works in steps of 64 q rows with double-buffered scores; `sub_block`
   // is accepted for compatibility and does not change the tiling.
   if (p->head_dim == 64) return p->head_dim_v == 64 ? launch_bwd_col<64, 64, false>(*p, st) : launch_bwd_col<64, 128, false>(*p, st);
@@ -138,6 +147,7 @@ extern "C" int splash_bwd_fused(const SplashParams* p, void* stream) {
   if (!p->dq || !p->dk || !p->dv || !p->dq_acc) return fail(SPLASH_INVALID_ARGUMENT, "dq, dk, dv and dq_acc must be non-null");
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (int rc = launch_seg_ranges(*p, st)) return rc;
   if (p->out) {
     // One pass streams O and dO for delta and clears the accumulator on the way.
     if (int rc = launch_delta(p->out, p->d_out, p->delta, static_cast<long long>(p->batch) * p->heads * p->q_len,

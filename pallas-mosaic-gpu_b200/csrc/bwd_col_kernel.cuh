@@ -35,6 +35,7 @@
 #include "../../include/splash_sm100.h"
 #include "fwd_kernel.cuh"  // math constants
 #include "ptx.cuh"
+#include "seg_skip.cuh"
 
 namespace splash {
 
@@ -47,6 +48,9 @@ struct BwdArgs {
   const int32_t* mask_desc;
   const int32_t* seg_q;
   const int32_t* seg_kv;
+  const uint8_t* partial_blocks;  // bit-packed dense partial blocks [n, 128, 16 bytes], or null
+  const int2* seg_q_ranges;   // [batch, q_len / 64] (min, max) segment ids, or null: no block skipping
+  const int2* seg_kv_ranges;  // [batch, kv_len / 64]
   const float* lse;
   const float* delta;
   void* dq;
@@ -84,7 +88,7 @@ struct ColLayout {
   static constexpr int kQStage = BC * D * 2;
   static constexpr int kDoStage = BC * DV * 2;
   static constexpr int kVecStage = BC * 4;          // lse, delta, q segment ids: BC words each
-  static constexpr int kMaskStage = kRows * BC;     // int8, transposed block slice
+  static constexpr int kMaskStage = kRows * 128 / 8;  // a whole transposed block, one bit per element
   static constexpr int kDsStage = kRows * BC * 2;   // FUSED: dS^T as an MMA operand
   static constexpr int kDqStage = 128 * 32 * 4;     // FUSED: half a dQ^T tile (32 q columns), f32
   // Tensor memory columns: two S^T buffers, two dP^T buffers, dK, dV.  P^T lives in the
@@ -96,8 +100,10 @@ struct ColLayout {
   static constexpr int kThreads = kEwThreads + (FUSED ? 128 : 0) + 128;
   static_assert(kTmemUsed <= 512, "tensor memory budget");
 
-  __host__ __device__ static size_t smem_bytes(int stages, bool dense, bool seg) {
+  // `list_steps`: capacity of the list of block steps that survive segment skipping (0 = no list).
+  __host__ __device__ static size_t smem_bytes(int stages, bool dense, bool seg, int list_steps = 0) {
     size_t b = 1024;
+    b += (static_cast<size_t>(list_steps) * 2 + 15) & ~static_cast<size_t>(15);
     b += kKBytes + kKDupBytes + kVBytes;
     b += static_cast<size_t>(stages) * (kQStage + kDoStage + 2 * kVecStage);
     if (seg) b += static_cast<size_t>(stages) * kVecStage;
@@ -119,51 +125,68 @@ struct ColBarriers {
   uint32_t tmem_base;
   uint32_t abort_flag;
   uint32_t dead;
+  uint32_t n_eff;  // block steps left after segment skipping
 };
 
 #define SPLASH_CBAR(field, idx) \
   (bars_u32 + static_cast<uint32_t>(offsetof(ColBarriers, field)) + 8u * static_cast<uint32_t>(idx))
 
 // Enumerates the steps of one CTA: q heads of the group x visited q blocks x sub-blocks.
+// A "block step" is one (head, visited q block) pair, numbered in that order ("flat"
+// index); with segment skipping the CTA walks the list of surviving flat indices that one
+// of its warps put in shared memory, otherwise all of them.
 template <int SUB>
 struct ColSteps {
   const BwdArgs* a;
   int kj, head0, group;
-  int g, s, sb, n;
+  uint32_t list_u32;
+  bool has_list;
+  int count;   // block steps to walk
+  int e;       // position in that sequence
+  int g, s, sb, n, base;  // head, step inside the head, sub-step, steps of head g, flat index of (g, 0)
+  uint32_t entry;
 
   __device__ __forceinline__ int mask_head(int gg) const { return a->mask_heads > 1 ? head0 + gg : 0; }
   __device__ __forceinline__ int steps_of(int gg) const { return a->num_steps[mask_head(gg) * a->kv_blocks + kj]; }
-  __device__ __forceinline__ void skip_empty() {
-    while (g < group && n == 0) {
-      ++g;
-      if (g < group) n = steps_of(g);
-    }
-  }
-  __device__ __forceinline__ void init(const BwdArgs* args, int kj_, int head0_, int group_) {
+  __device__ __forceinline__ void bind(const BwdArgs* args, int kj_, int head0_, int group_) {
     a = args; kj = kj_; head0 = head0_; group = group_;
-    g = 0; s = 0; sb = 0;
-    n = steps_of(0);
-    skip_empty();
   }
-  __device__ __forceinline__ bool valid() const { return g < group; }
+  // Scheduled block steps of the CTA, before any skipping.
+  __device__ __forceinline__ int scheduled() const {
+    int t = 0;
+    for (int gg = 0; gg < group; ++gg) t += steps_of(gg);
+    return t;
+  }
+  // Offset into the step lists of flat index f (used while the list is being built).
+  __device__ __forceinline__ int off_of_flat(int f) const {
+    int gg = 0, bb = 0, nn = steps_of(0);
+    while (f >= bb + nn) { bb += nn; ++gg; nn = steps_of(gg); }
+    return (mask_head(gg) * a->kv_blocks + kj) * a->max_steps + (f - bb);
+  }
+  __device__ __forceinline__ void seek() {
+    entry = has_list ? lds16(list_u32 + 2u * e) : static_cast<uint32_t>(e);
+    const int flat = static_cast<int>(entry & 0x7fffu);
+    while (flat >= base + n) { base += n; ++g; n = steps_of(g); }
+    s = flat - base;
+  }
+  __device__ __forceinline__ void start(uint32_t list, bool with_list, int count_) {
+    list_u32 = list; has_list = with_list; count = count_;
+    e = 0; g = 0; s = 0; sb = 0; base = 0; entry = 0;
+    n = steps_of(0);
+    if (count > 0) seek();
+  }
+  __device__ __forceinline__ bool valid() const { return e < count; }
   __device__ __forceinline__ void next() {
     if (++sb == SUB) {
       sb = 0;
-      if (++s == n) {
-        s = 0;
-        ++g;
-        if (g < group) n = steps_of(g);
-        skip_empty();
-      }
+      if (++e < count) seek();
     }
   }
   __device__ __forceinline__ int head() const { return head0 + g; }
   __device__ __forceinline__ int off() const { return (mask_head(g) * a->kv_blocks + kj) * a->max_steps + s; }
-  __device__ __forceinline__ int total() const {
-    int t = 0;
-    for (int gg = 0; gg < group; ++gg) t += steps_of(gg);
-    return t * SUB;
-  }
+  __device__ __forceinline__ int total() const { return count * SUB; }
+  // Both sides of the block carry one and the same segment id: nothing to compare.
+  __device__ __forceinline__ bool uniform() const { return has_list && (entry & kSegUniformBit); }
 };
 
 // PLAIN: no soft-cap, no segment ids, no streamed mask blocks -- that code is compiled out.
@@ -172,8 +195,7 @@ __global__ void __launch_bounds__(ColLayout<D, DV, FUSED>::kThreads, 1)
 splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
                       const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv,
-                      const __grid_constant__ CUtensorMap tm_mask, const __grid_constant__ CUtensorMap tm_dqacc,
-                      const BwdArgs a) {
+                      const __grid_constant__ CUtensorMap tm_dqacc, const BwdArgs a) {
   using L = ColLayout<D, DV, FUSED>;
   constexpr int kRows = 128;
   constexpr int BC = kColBC;
@@ -198,6 +220,9 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const uint32_t delta_u32 = lse_u32 + stages * L::kVecStage;
   const uint32_t segq_u32 = delta_u32 + stages * L::kVecStage;
   const uint32_t bars_u32 = (segq_u32 + (has_seg ? stages * L::kVecStage : 0) + 15u) & ~15u;
+  const uint32_t list_u32 = (bars_u32 + static_cast<uint32_t>(sizeof(ColBarriers)) + 15u) & ~15u;  // surviving block steps
+  const uint32_t neff_u32 = bars_u32 + static_cast<uint32_t>(offsetof(ColBarriers, n_eff));
+  const bool has_list = has_seg && a.seg_q_ranges != nullptr;
   const uint32_t abort_u32 = bars_u32 + static_cast<uint32_t>(offsetof(ColBarriers, abort_flag));
   const uint32_t tmem_slot_u32 = bars_u32 + static_cast<uint32_t>(offsetof(ColBarriers, tmem_base));
   const uint32_t dead_u32 = bars_u32 + static_cast<uint32_t>(offsetof(ColBarriers, dead));
@@ -217,8 +242,8 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const int kv_row0 = (b * a.kv_heads + kvh) * a.kv_len + kj * kRows;  // row in the [B*KVH*Skv, D] view
 
   ColSteps<kSub> it;
-  it.init(&a, kj, head0, group);
-  const int total = it.total();
+  it.bind(&a, kj, head0, group);
+  const int scheduled = it.scheduled();
 
   // One warp initialises the barriers, a lane each, while the MMA warp allocates tensor
   // memory; one CTA barrier later every role starts.  A launch that finds the status
@@ -243,12 +268,24 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   } else if (warp == kProducerWarp0 + 1) {
     tmem_alloc(tmem_slot_u32, L::kTmemCols);
     tmem_relinquish();
+  } else if (warp == 1 && has_list) {
+    // Block steps whose q and kv segment-id ranges can meet; the others are left out by every role.
+    const int2* qt = a.seg_q_ranges + static_cast<size_t>(b) * (a.q_len / kSegChunk);
+    const int2* kt = a.seg_kv_ranges + static_cast<size_t>(b) * (a.kv_len / kSegChunk);
+    const SegRange kr = seg_range(kt, kj * (kRows / kSegChunk), kRows / kSegChunk);
+    const int kept = build_step_list(list_u32, scheduled, lane, [&](int f) {
+      const int qblk = a.block_list[it.off_of_flat(f)];
+      return seg_classify(seg_range(qt, qblk * (128 / kSegChunk), 128 / kSegChunk), kr);
+    });
+    if (lane == 0) sts32(neff_u32, static_cast<uint32_t>(kept));
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = lds32(tmem_slot_u32);
   const WaitCtx ctx{abort_u32};
+  it.start(list_u32, has_list, has_list ? static_cast<int>(lds32(neff_u32)) : scheduled);
+  const int total = it.total();
   if (lds32(dead_u32)) {
     if (warp == kProducerWarp0 + 1) {
       __syncwarp();
@@ -285,7 +322,7 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         const uint32_t bytes = L::kQStage + L::kDoStage + 2 * L::kVecStage + (has_seg ? L::kVecStage : 0) +
                                (partial_dense ? L::kMaskStage : 0);
         const uint32_t bar = SPLASH_CBAR(full, slot);
-        const int mrow = partial_dense ? a.mask_block[off] * 128 : 0;
+        const size_t mblock = partial_dense ? static_cast<size_t>(a.mask_block[off]) : 0;
         if (elect_one()) {
           mbar_arrive_expect_tx(bar, bytes);
 #pragma unroll
@@ -299,7 +336,8 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           if (has_seg)
             bulk_load_1d(segq_u32 + slot * L::kVecStage,
                          a.seg_q + static_cast<size_t>(b) * a.q_len + qblk * 128 + it.sb * BC, L::kVecStage, bar);
-          if (partial_dense) tma_load_2d(mask_u32 + slot * L::kMaskStage, &tm_mask, it.sb * BC, mrow, bar);
+          if (partial_dense)
+            bulk_load_1d(mask_u32 + slot * L::kMaskStage, a.partial_blocks + mblock * L::kMaskStage, L::kMaskStage, bar);
         }
         if (++slot == stages) { slot = 0; phase ^= 1; }
       }
@@ -506,9 +544,10 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           tmem_wait_ld();
           uint32_t ppk[16], dspk[16];
           const uint32_t vec_off = slot * L::kVecStage + (col0 + c * 32) * 4;
-          if (!partial && !has_seg && !cap_on) {
-            // FULL block, no segment ids, no soft-cap: nothing to mask.  (A row whose lse
-            // is mask_value never meets a FULL block, so no guard is needed here.)
+          if (!partial && (!has_seg || it.uniform()) && !cap_on) {
+            // FULL block, no segment ids (or one id on both sides), no soft-cap: nothing to
+            // mask.  (A row whose lse is mask_value never meets such a block, so no guard is
+            // needed here.)
 #pragma unroll
             for (int g = 0; g < 8; ++g) {
               const uint4 lw = lds128(lse_u32 + vec_off + g * 16);
@@ -537,19 +576,10 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
               }
             }
             if (partial && has_dense) {
-              // Transposed block slice: rows = kv, BC bytes per row, TMA-swizzled.
-#pragma unroll
-              for (int g = 0; g < 2; ++g) {
-                uint32_t o = row * BC + col0 + c * 32 + g * 16;
-                o ^= ((o >> 7) & (BC == 128 ? 7u : 3u)) << 4;
-                const uint4 wd = lds128(mask_u32 + slot * L::kMaskStage + o);
-                const uint32_t ww[4] = {wd.x, wd.y, wd.z, wd.w};
-#pragma unroll
-                for (int e = 0; e < 16; ++e)
-                  if (((ww[e >> 2] >> ((e & 3) * 8)) & 0xff) == 0) vis &= ~(1u << (g * 16 + e));
-              }
+              // Transposed block, one bit per element: 16 bytes per kv row, bit = q column.
+              vis &= lds32(mask_u32 + slot * L::kMaskStage + row * 16 + (it.sb * BC + col0 + c * 32) / 8);
             }
-            if (has_seg) {
+            if (has_seg && !it.uniform()) {
 #pragma unroll
               for (int g = 0; g < 8; ++g) {
                 const uint4 sg = lds128(segq_u32 + vec_off + g * 16);
@@ -577,7 +607,7 @@ splash_bwd_col_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 }
                 // Rows that saw no key carry lse = mask_value; they contribute nothing.
                 const bool on = ((vis >> i) & 1u) && lses[e] != a.mask_value;
-                const float p = on ? ex2_approx((sval - lses[e]) * kLog2e) : 0.f;
+                const float p = on ? ex2_approx(fmaf(sval, kLog2e, lses[e] * -kLog2e)) : 0.f;  // same rounding as the unmasked path
                 float ds = p * (__uint_as_float(dpraw[i]) - dels[e]);
                 if (cap_on) ds *= (1.f - tanh_v * tanh_v);
                 pv[e] = p;

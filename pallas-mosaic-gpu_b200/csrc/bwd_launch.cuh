@@ -3,6 +3,7 @@
 
 #include "bwd_col_kernel.cuh"
 #include "bwd_row_kernel.cuh"
+#include "dispatch.h"
 #include "host_common.cuh"
 
 namespace splash {
@@ -16,6 +17,9 @@ inline void fill_bwd_args(BwdArgs& a, const SplashParams& p, bool dense, bool se
   a.mask_desc = p.mask_desc;
   a.seg_q = p.seg_q;
   a.seg_kv = p.seg_kv;
+  a.partial_blocks = reinterpret_cast<const uint8_t*>(p.partial_blocks);
+  a.seg_q_ranges = nullptr;
+  a.seg_kv_ranges = nullptr;
   a.lse = p.lse;
   a.delta = p.delta;
   a.dq = p.dq;
@@ -49,7 +53,12 @@ int launch_bwd_col_typed(const SplashParams& p, cudaStream_t stream) {
   // three stages (or the caller's larger request) are used when they fit, two otherwise.
   int stages = p.num_stages < 3 ? 3 : (p.num_stages > kBwdMaxStages ? kBwdMaxStages : p.num_stages);
   while (stages > 2 && L::smem_bytes(stages, dense, seg) > kMaxDynamicSmem) --stages;
-  const size_t smem = L::smem_bytes(stages, dense, seg);
+  // Segment skipping keeps a list of up to group * max_steps block steps per CTA (16-bit entries);
+  // without room for it every scheduled block is computed.
+  const int list_steps = (p.heads / p.kv_heads) * p.max_steps;
+  const bool skipping = seg && p.seg_ranges != nullptr && list_steps < (1 << 15) &&
+                        L::smem_bytes(stages, dense, seg, list_steps) <= kMaxDynamicSmem;
+  const size_t smem = L::smem_bytes(stages, dense, seg, skipping ? list_steps : 0);
   if (smem > kMaxDynamicSmem) {
     char d[96];
     snprintf(d, sizeof d, "%zu > %zu bytes", smem, kMaxDynamicSmem);
@@ -58,9 +67,10 @@ int launch_bwd_col_typed(const SplashParams& p, cudaStream_t stream) {
   const CUtensorMapDataType dt = tmap_dtype(p.dtype);
   const uint64_t q_rows = static_cast<uint64_t>(p.batch) * p.heads * p.q_len;
   const uint64_t kv_rows = static_cast<uint64_t>(p.batch) * p.kv_heads * p.kv_len;
-  CUtensorMap tm_q, tm_k, tm_v, tm_do, tm_dk, tm_dv, tm_mask, tm_dqacc;
-  memset(&tm_mask, 0, sizeof tm_mask);
+  CUtensorMap tm_q, tm_k, tm_v, tm_do, tm_dk, tm_dv, tm_dqacc;
   memset(&tm_dqacc, 0, sizeof tm_dqacc);
+  if (dense && (reinterpret_cast<uintptr_t>(p.partial_blocks) & 15))
+    return fail(SPLASH_INVALID_ARGUMENT, "partial_blocks not 16-byte aligned");
   int rc;
   if ((rc = make_tmap_2d(&tm_q, p.q, dt, 2, q_rows, D, BC, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if ((rc = make_tmap_2d(&tm_do, p.d_out, dt, 2, q_rows, DV, BC, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
@@ -68,12 +78,6 @@ int launch_bwd_col_typed(const SplashParams& p, cudaStream_t stream) {
   if ((rc = make_tmap_2d(&tm_v, p.v, dt, 2, kv_rows, DV, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if ((rc = make_tmap_2d(&tm_dk, p.dk, dt, 2, kv_rows, D, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if ((rc = make_tmap_2d(&tm_dv, p.dv, dt, 2, kv_rows, DV, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
-  if (dense) {
-    const uint64_t mrows = static_cast<uint64_t>(p.num_partial_blocks) * 128;
-    if ((rc = make_tmap_2d(&tm_mask, p.partial_blocks, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, mrows, 128, 128, BC,
-                           CU_TENSOR_MAP_SWIZZLE_64B)))
-      return rc;
-  }
   if (FUSED) {
     // f32 accumulator viewed as [batch * heads * head_dim, q_len]; tiles of 32 q columns.
     const uint64_t acc_rows = static_cast<uint64_t>(p.batch) * p.heads * D;
@@ -84,12 +88,14 @@ int launch_bwd_col_typed(const SplashParams& p, cudaStream_t stream) {
   BwdArgs a;
   fill_bwd_args(a, p, dense, seg);
   a.stages = stages;
+  a.seg_q_ranges = skipping ? seg_q_ranges(p) : nullptr;
+  a.seg_kv_ranges = skipping ? seg_kv_ranges(p) : nullptr;
   // The kernel without its soft-cap, segment and streamed-mask code when the call uses none.
   const bool plain = p.soft_cap == 0.f && !seg && !dense;
   auto kernel = plain ? splash_bwd_col_kernel<D, DV, FUSED, true, BF16> : splash_bwd_col_kernel<D, DV, FUSED, false, BF16>;
   if ((rc = opt_in_smem(kernel, smem))) return rc;
   const unsigned grid = static_cast<unsigned>(a.kv_blocks) * p.kv_heads * p.batch;
-  kernel<<<grid, L::kThreads, smem, stream>>>(tm_q, tm_k, tm_v, tm_do, tm_dk, tm_dv, tm_mask, tm_dqacc, a);
+  kernel<<<grid, L::kThreads, smem, stream>>>(tm_q, tm_k, tm_v, tm_do, tm_dk, tm_dv, tm_dqacc, a);
   SPLASH_CUDA_CHECK(cudaGetLastError());
   return SPLASH_OK;
 }
@@ -119,26 +125,21 @@ int launch_bwd_row_typed(const SplashParams& p, cudaStream_t stream) {
   const CUtensorMapDataType dt = tmap_dtype(p.dtype);
   const uint64_t q_rows = static_cast<uint64_t>(p.batch) * p.heads * p.q_len;
   const uint64_t kv_rows = static_cast<uint64_t>(p.batch) * p.kv_heads * p.kv_len;
-  CUtensorMap tm_q, tm_k, tm_v, tm_do, tm_dq, tm_mask;
-  memset(&tm_mask, 0, sizeof tm_mask);
+  CUtensorMap tm_q, tm_k, tm_v, tm_do, tm_dq;
+  if (dense && (reinterpret_cast<uintptr_t>(p.partial_blocks) & 15))
+    return fail(SPLASH_INVALID_ARGUMENT, "partial_blocks not 16-byte aligned");
   int rc;
   if ((rc = make_tmap_2d(&tm_q, p.q, dt, 2, q_rows, D, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if ((rc = make_tmap_2d(&tm_do, p.d_out, dt, 2, q_rows, DV, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if ((rc = make_tmap_2d(&tm_k, p.k, dt, 2, kv_rows, D, BC, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if ((rc = make_tmap_2d(&tm_v, p.v, dt, 2, kv_rows, DV, BC, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if ((rc = make_tmap_2d(&tm_dq, p.dq, dt, 2, q_rows, D, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
-  if (dense) {
-    const uint64_t mrows = static_cast<uint64_t>(p.num_partial_blocks) * 128;
-    if ((rc = make_tmap_2d(&tm_mask, p.partial_blocks, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, mrows, 128, 128, BC,
-                           BC == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B)))
-      return rc;
-  }
   BwdArgs a;
   fill_bwd_args(a, p, dense, seg);
   auto kernel = splash_bwd_row_kernel<D, DV, BC, BF16>;
   if ((rc = opt_in_smem(kernel, smem))) return rc;
   const unsigned grid = static_cast<unsigned>(a.q_blocks) * p.heads * p.batch;
-  kernel<<<grid, L::kThreads, smem, stream>>>(tm_q, tm_k, tm_v, tm_do, tm_dq, tm_mask, a);
+  kernel<<<grid, L::kThreads, smem, stream>>>(tm_q, tm_k, tm_v, tm_do, tm_dq, a);
   SPLASH_CUDA_CHECK(cudaGetLastError());
   return SPLASH_OK;
 }

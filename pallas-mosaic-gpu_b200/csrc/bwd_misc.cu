@@ -126,6 +126,37 @@ __global__ void __launch_bounds__(256) dq_transpose_cast_kernel(const float* __r
   }
 }
 
+// (min, max) of every 64 consecutive segment ids: one warp per chunk, two ids per lane.
+// `out` holds the q part [batch, q_len / 64] followed by the kv part [batch, kv_len / 64].
+__global__ void __launch_bounds__(256) seg_ranges_kernel(const int32_t* __restrict__ seg_q,
+                                                         const int32_t* __restrict__ seg_kv, int2* __restrict__ out,
+                                                         long long q_chunks, long long kv_chunks) {
+  const long long chunk = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (chunk >= q_chunks + kv_chunks) return;
+  const int32_t* src = chunk < q_chunks ? seg_q + chunk * 64 : seg_kv + (chunk - q_chunks) * 64;
+  const int2 v = *reinterpret_cast<const int2*>(src + 2 * lane);
+  int lo = min(v.x, v.y), hi = max(v.x, v.y);
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) {
+    lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, s));
+    hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, s));
+  }
+  if (lane == 0) out[chunk] = make_int2(lo, hi);
+}
+
+int launch_seg_ranges(const SplashParams& p, cudaStream_t stream) {
+  if (!p.seg_q || !p.seg_kv || !p.seg_ranges) return SPLASH_OK;
+  if (p.q_len % 64 || p.kv_len % 64) return fail(SPLASH_INVALID_ARGUMENT, "segment ranges need sequence lengths that are multiples of 64");
+  const long long q_chunks = static_cast<long long>(p.batch) * (p.q_len / 64);
+  const long long kv_chunks = static_cast<long long>(p.batch) * (p.kv_len / 64);
+  const unsigned grid = static_cast<unsigned>((q_chunks + kv_chunks + 7) / 8);
+  seg_ranges_kernel<<<grid, 256, 0, stream>>>(p.seg_q, p.seg_kv, reinterpret_cast<int2*>(p.seg_ranges), q_chunks,
+                                               kv_chunks);
+  SPLASH_CUDA_CHECK(cudaGetLastError());
+  return SPLASH_OK;
+}
+
 int launch_dq_transpose_cast(const float* acc, void* dq, long long batch_heads, int head_dim, int q_len, int dtype,
                              cudaStream_t stream) {
   if (!acc || !dq || head_dim % 64 || q_len % 64) return fail(SPLASH_INVALID_ARGUMENT, "bad dq cast arguments");

@@ -37,7 +37,7 @@ struct RowLayout {
   static constexpr int kKStage = BC * D * 2;
   static constexpr int kVStage = BC * DV * 2;
   static constexpr int kVecStage = BC * 4;       // kv segment ids
-  static constexpr int kMaskStage = kRows * BC;  // int8 block slice
+  static constexpr int kMaskStage = kRows * 128 / 8;  // a whole block, one bit per element
   static constexpr int kColS = 0, kColDp = BC, kColDs = 2 * BC, kColDq = 3 * BC;  // two dS buffers of BC/2
   static constexpr int kTmemUsed = 3 * BC + D;
   static constexpr int kTmemCols = kTmemUsed <= 256 ? 256 : 512;
@@ -72,8 +72,7 @@ template <int D, int DV, int BC, bool BF16>
 __global__ void __launch_bounds__(384, 1)
 splash_bwd_row_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
-                      const __grid_constant__ CUtensorMap tm_dq, const __grid_constant__ CUtensorMap tm_mask,
-                      const BwdArgs a) {
+                      const __grid_constant__ CUtensorMap tm_dq, const BwdArgs a) {
   using L = RowLayout<D, DV, BC>;
   constexpr int kRows = 128;
   constexpr int kSub = L::kSub;
@@ -162,7 +161,7 @@ splash_bwd_row_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         const uint32_t bytes = L::kKStage + L::kVStage + (a.has_seg ? L::kVecStage : 0) +
                                (partial_dense ? L::kMaskStage : 0);
         const uint32_t bar = SPLASH_RBAR(full, slot);
-        const int mrow = partial_dense ? a.mask_block[sched_off + s] * 128 : 0;
+        const size_t mblock = partial_dense ? static_cast<size_t>(a.mask_block[sched_off + s]) : 0;
         if (elect_one()) {
           mbar_arrive_expect_tx(bar, bytes);
 #pragma unroll
@@ -174,7 +173,8 @@ splash_bwd_row_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           if (a.has_seg)
             bulk_load_1d(seg_u32 + slot * L::kVecStage,
                          a.seg_kv + static_cast<size_t>(b) * a.kv_len + j * 128 + sb * BC, L::kVecStage, bar);
-          if (partial_dense) tma_load_2d(mask_u32 + slot * L::kMaskStage, &tm_mask, sb * BC, mrow, bar);
+          if (partial_dense)
+            bulk_load_1d(mask_u32 + slot * L::kMaskStage, a.partial_blocks + mblock * L::kMaskStage, L::kMaskStage, bar);
         }
         if (++slot == stages) { slot = 0; phase ^= 1; }
       }
@@ -298,16 +298,8 @@ splash_bwd_row_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             }
           }
           if (partial && a.has_dense) {
-#pragma unroll
-            for (int g = 0; g < 2; ++g) {
-              uint32_t o = row * BC + col0 + c * 32 + g * 16;
-              o ^= ((o >> 7) & (BC == 128 ? 7u : 3u)) << 4;
-              const uint4 wd = lds128(mask_u32 + slot * L::kMaskStage + o);
-              const uint32_t ww[4] = {wd.x, wd.y, wd.z, wd.w};
-#pragma unroll
-              for (int e = 0; e < 16; ++e)
-                if (((ww[e >> 2] >> ((e & 3) * 8)) & 0xff) == 0) vis &= ~(1u << (g * 16 + e));
-            }
+            // One bit per element: 16 bytes per q row, bit = kv column inside the block.
+            vis &= lds32(mask_u32 + slot * L::kMaskStage + row * 16 + (sb * BC + col0 + c * 32) / 8);
           }
           if (a.has_seg) {
 #pragma unroll

@@ -32,6 +32,10 @@ static int launch_bwd_wide_typed(const SplashParams& p, cudaStream_t stream) {
   BwdArgs a;
   fill_bwd_args(a, p, false, seg);
   a.stages = L::kSlots;
+  // Segment skipping when the CTA's list of block steps fits the room set aside for it.
+  const bool skipping = seg && p.seg_ranges != nullptr && (p.heads / p.kv_heads) * p.max_steps <= L::kListSteps;
+  a.seg_q_ranges = skipping ? seg_q_ranges(p) : nullptr;
+  a.seg_kv_ranges = skipping ? seg_kv_ranges(p) : nullptr;
   const bool plain = p.soft_cap == 0.f && !seg;
   auto kernel = plain ? splash_bwd_wide_kernel<true, BF16> : splash_bwd_wide_kernel<false, BF16>;
   if ((rc = opt_in_smem(kernel, L::kSmemBytes))) return rc;

@@ -74,7 +74,9 @@ struct WideLayout {
   static constexpr int kOffLse = 7 * kTile, kOffDelta = kOffLse + kSlots * kVecBytes;
   static constexpr int kOffBars = kOffDelta + kSlots * kVecBytes;
   static constexpr int kBarBytes = 256;
-  static constexpr int kSmemBytes = kOffBars + kBarBytes;
+  static constexpr int kListSteps = 256;  // capacity of the list of block steps that survive segment skipping
+  static constexpr int kOffList = kOffBars + kBarBytes;
+  static constexpr int kSmemBytes = kOffList + kListSteps * 2;
   // Tensor memory columns.
   static constexpr int kColS = 0, kColDp = 128, kColDk = 256, kColDv = 384;
   static constexpr int kTmemCols = 512;
@@ -93,6 +95,7 @@ struct WideBarriers {
   uint32_t tmem_base;
   uint32_t abort_flag;
   uint32_t dead;
+  uint32_t n_eff;  // block steps left after segment skipping
 };
 static_assert(sizeof(WideBarriers) <= WideLayout::kBarBytes, "barrier block");
 
@@ -130,6 +133,9 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   const uint32_t abort_u32 = bars_u32 + static_cast<uint32_t>(offsetof(WideBarriers, abort_flag));
   const uint32_t dead_u32 = bars_u32 + static_cast<uint32_t>(offsetof(WideBarriers, dead));
   const uint32_t tmem_slot_u32 = bars_u32 + static_cast<uint32_t>(offsetof(WideBarriers, tmem_base));
+  const uint32_t neff_u32 = bars_u32 + static_cast<uint32_t>(offsetof(WideBarriers, n_eff));
+  const uint32_t list_u32 = base_u32 + L::kOffList;
+  const bool has_list = has_seg && a.seg_q_ranges != nullptr;
 
   const int warp = uniform_warp_index();
   const int lane = threadIdx.x & 31;
@@ -146,8 +152,8 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   const int kv_row0 = (b * a.kv_heads + kvh) * a.kv_len + kj * kRows;  // row in the [B*KVH*Skv, D] view
 
   ColSteps<1> it;
-  it.init(&a, kj, head0, group);
-  const int total = it.total();
+  it.bind(&a, kj, head0, group);
+  const int scheduled = it.scheduled();
 
   // One warp initialises the barriers while the MMA warp allocates tensor memory.  Thread
   // 0 reads the status word once and shares it, so the whole CTA agrees on whether an
@@ -181,12 +187,24 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   } else if (warp == kProducerWarp0 + 1) {
     tmem_alloc(tmem_slot_u32, L::kTmemCols);
     tmem_relinquish();
+  } else if (warp == 1 && has_list) {
+    // Block steps whose q and kv segment-id ranges can meet; the others are left out by every role.
+    const int2* qt = a.seg_q_ranges + static_cast<size_t>(b) * (a.q_len / kSegChunk);
+    const int2* kt = a.seg_kv_ranges + static_cast<size_t>(b) * (a.kv_len / kSegChunk);
+    const SegRange kr = seg_range(kt, kj * (kRows / kSegChunk), kRows / kSegChunk);
+    const int kept = build_step_list(list_u32, scheduled, lane, [&](int f) {
+      const int qblk = a.block_list[it.off_of_flat(f)];
+      return seg_classify(seg_range(qt, qblk * (128 / kSegChunk), 128 / kSegChunk), kr);
+    });
+    if (lane == 0) sts32(neff_u32, static_cast<uint32_t>(kept));
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = lds32(tmem_slot_u32);
   const WaitCtx ctx{abort_u32};
+  it.start(list_u32, has_list, has_list ? static_cast<int>(lds32(neff_u32)) : scheduled);
+  const int total = it.total();
   if (lds32(dead_u32)) {
     if (warp == kProducerWarp0 + 1) {
       __syncwarp();
@@ -412,7 +430,8 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         const int q0 = qblk * 128 + col0;  // sequence position of this thread's first column
         // Visibility of this thread's 64 columns (bit i of word c: column c * 32 + i).
         uint32_t vis[2] = {0xffffffffu, 0xffffffffu};
-        const bool plain_step = !partial && !has_seg && !cap_on;
+        const bool seg_compare = has_seg && !it.uniform();
+        const bool plain_step = !partial && !seg_compare && !cap_on;
         if (!plain_step) {
           if (partial) {
             // Column i of word c is visible iff band_lo <= d0 - i <= band_hi: a run of bits.
@@ -423,7 +442,7 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
               vis[c] = first <= last ? ((0xffffffffu >> (31 - last)) & (0xffffffffu << first)) : 0u;
             }
           }
-          if (has_seg) {
+          if (seg_compare) {
             const int4* sq = reinterpret_cast<const int4*>(a.seg_q + static_cast<size_t>(b) * a.q_len + q0);
 #pragma unroll
             for (int g = 0; g < 16; ++g) {
@@ -491,7 +510,7 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           };
           using T = std::true_type;
           using F = std::false_type;
-          const bool masked = partial || has_seg;
+          const bool masked = partial || seg_compare;
           if (!cap_on && !masked) body(F{}, F{});
           else if (!cap_on) body(F{}, T{});
           else if (!masked) body(T{}, F{});

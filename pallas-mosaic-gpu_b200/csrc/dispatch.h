@@ -34,5 +34,17 @@ int launch_delta(const void* o, const void* d_out, float* delta, long long rows,
                  cudaStream_t stream, float* zero = nullptr, int zero_floats_per_row = 0);
 int launch_dq_transpose_cast(const float* acc, void* dq, long long batch_heads, int head_dim, int q_len, int dtype,
                              cudaStream_t stream);
+// Fills p.seg_ranges (when given, with segment ids) with the (min, max) id of every 64 positions.
+int launch_seg_ranges(const SplashParams& p, cudaStream_t stream);
+
+// The two halves of p.seg_ranges as the kernels read them, or nulls when skipping is off.
+inline const int2* seg_q_ranges(const SplashParams& p) {
+  return (p.seg_q && p.seg_ranges) ? reinterpret_cast<const int2*>(p.seg_ranges) : nullptr;
+}
+inline const int2* seg_kv_ranges(const SplashParams& p) {
+  return (p.seg_q && p.seg_ranges)
+             ? reinterpret_cast<const int2*>(p.seg_ranges) + static_cast<long long>(p.batch) * (p.q_len / 64)
+             : nullptr;
+}
 
 }  // namespace splash

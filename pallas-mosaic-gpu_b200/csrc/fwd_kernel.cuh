@@ -39,6 +39,7 @@
 
 #include "../../include/splash_sm100.h"
 #include "ptx.cuh"
+#include "seg_skip.cuh"
 
 namespace splash {
 
@@ -55,6 +56,9 @@ struct FwdArgs {
   const int32_t* mask_desc;
   const int32_t* seg_q;
   const int32_t* seg_kv;
+  const uint8_t* partial_blocks;  // bit-packed dense partial blocks [n, block_q, block_kv / 8], or null
+  const int2* seg_q_ranges;   // [batch, q_len / 64] (min, max) segment ids, or null: no block skipping
+  const int2* seg_kv_ranges;  // [batch, kv_len / 64]
   void* out;
   float* lse_out;
   int32_t* status;
@@ -80,7 +84,7 @@ struct FwdLayout {
   static constexpr int kQBytes = NT * kTile * D * 2;
   static constexpr int kKStage = BKV * D * 2;
   static constexpr int kVStage = BKV * DV * 2;
-  static constexpr int kMaskStage = NT * kTile * BKV;
+  static constexpr int kMaskStage = NT * kTile * BKV / 8;  // one bit per element
   static constexpr int kSegStage = BKV * 4;
   // Tensor-memory columns: S (two buffers) | P when it has columns of its own | O.
   // P lies over its S except with alternating warpgroups, where freeing S(t) as soon as
@@ -102,13 +106,15 @@ struct FwdLayout {
   static constexpr int kSoftmaxRegs = 216;
   static constexpr int kProducerRegs = 72;
 
-  __host__ __device__ static size_t smem_bytes(int stages, bool dense, bool seg) {
+  // `list_steps`: capacity of the list of steps that survive segment skipping (0 = no list).
+  __host__ __device__ static size_t smem_bytes(int stages, bool dense, bool seg, int list_steps = 0) {
     size_t b = 1024;  // alignment slack
     b += kQBytes + static_cast<size_t>(stages) * (kKStage + kVStage);
     if (dense) b += static_cast<size_t>(stages) * kMaskStage;
     if (seg) b += static_cast<size_t>(stages) * kSegStage;
     b += 1024;  // barriers, TMEM slot, flags
     b += kShareBytes;
+    b += (static_cast<size_t>(list_steps) * 2 + 15) & ~static_cast<size_t>(15);
     return b;
   }
 };
@@ -129,6 +135,7 @@ struct FwdBarriers {
   uint32_t tmem_base;
   uint32_t abort_flag;
   uint32_t dead;
+  uint32_t n_eff;  // steps left after segment skipping
 };
 
 #define SPLASH_BAR(field, idx) \
@@ -140,7 +147,7 @@ template <int D, int DV, int BKV, int NT, int AW, bool PLAIN, bool BF16>
 __global__ void __launch_bounds__((NT * AW + 1) * 128, 1)
 splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                   const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
-                  const __grid_constant__ CUtensorMap tm_mask, const FwdArgs a) {
+                  const FwdArgs a) {
   using L = FwdLayout<D, DV, BKV, NT, AW>;
   constexpr int kTile = 128;
   constexpr int kBq = NT * kTile;
@@ -162,6 +169,9 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const uint32_t abort_u32 = bars_u32 + static_cast<uint32_t>(offsetof(FwdBarriers, abort_flag));
   const uint32_t tmem_slot_u32 = bars_u32 + static_cast<uint32_t>(offsetof(FwdBarriers, tmem_base));
   const uint32_t dead_u32 = bars_u32 + static_cast<uint32_t>(offsetof(FwdBarriers, dead));
+  const uint32_t neff_u32 = bars_u32 + static_cast<uint32_t>(offsetof(FwdBarriers, n_eff));
+  const uint32_t list_u32 = share_u32 + L::kShareBytes;  // surviving steps, 16 bits each
+  const bool has_list = has_seg && a.seg_q_ranges != nullptr;
 
   const int warp = uniform_warp_index();
   const int lane = threadIdx.x & 31;
@@ -173,7 +183,7 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const int b = hb / a.heads;
   const int mh = a.mask_heads > 1 ? h : 0;
   const int qi = a.block_order[mh * a.q_blocks + order_idx];
-  const int n = a.num_steps[mh * a.q_blocks + qi];
+  const int n_sched = a.num_steps[mh * a.q_blocks + qi];
   const bool has_aux = has_dense || has_seg;
   const int sched_off = (mh * a.q_blocks + qi) * a.max_steps;  // offset into the step lists
   const int q_row0 = (b * a.heads + h) * a.q_len + qi * kBq;   // row in the [B*H*Sq, D] view
@@ -204,12 +214,26 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   } else if (warp == kSoftmaxWarps + 1) {
     tmem_alloc(tmem_slot_u32, L::kTmemCols);
     tmem_relinquish();
+  } else if (warp == 1 && has_list) {
+    // Steps whose q and kv segment-id ranges can meet; the others are left out by every role.
+    const int2* qt = a.seg_q_ranges + static_cast<size_t>(b) * (a.q_len / kSegChunk);
+    const int2* kt = a.seg_kv_ranges + static_cast<size_t>(b) * (a.kv_len / kSegChunk);
+    const SegRange qr = seg_range(qt, qi * (kBq / kSegChunk), kBq / kSegChunk);
+    const int kept = build_step_list(list_u32, n_sched, lane, [&](int s) {
+      const int j = a.block_list[sched_off + s];
+      return seg_classify(qr, seg_range(kt, j * (BKV / kSegChunk), BKV / kSegChunk));
+    });
+    if (lane == 0) sts32(neff_u32, static_cast<uint32_t>(kept));
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = lds32(tmem_slot_u32);
   const WaitCtx ctx{abort_u32};
+  const int n = has_list ? static_cast<int>(lds32(neff_u32)) : n_sched;
+  // Entry e of the CTA's step sequence: index into the schedule lists, and whether the
+  // block needs no segment comparison.
+  auto step_at = [&](int e) -> uint32_t { return has_list ? lds16(list_u32 + 2u * e) : static_cast<uint32_t>(e); };
   if (lds32(dead_u32)) {
     if (warp == kSoftmaxWarps + 1) {
       __syncwarp();
@@ -243,10 +267,14 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       }
       int slot = 0;
       uint32_t phase = 0;
-      int j_next = a.block_list[sched_off];
+      int st_next = static_cast<int>(step_at(0) & 0x7fffu);
+      int j_next = a.block_list[sched_off + st_next];
       for (int s = 0; s < n; ++s) {
-        const int j = j_next;
-        if (s + 1 < n) j_next = a.block_list[sched_off + s + 1];
+        const int j = j_next, st = st_next;
+        if (s + 1 < n) {
+          st_next = static_cast<int>(step_at(s + 1) & 0x7fffu);
+          j_next = a.block_list[sched_off + st_next];
+        }
         const int kv_row = kv_row0 + j * BKV;
         if (s >= stages && !warp_wait(SPLASH_BAR(k_empty, slot), phase ^ 1, ctx, kSiteTmaKEmpty, s)) break;
         if (elect_one()) {
@@ -257,20 +285,17 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
         if (has_aux) {
           if (s >= stages && !warp_wait(SPLASH_BAR(aux_empty, slot), phase ^ 1, ctx, kSiteTmaAuxEmpty, s)) break;
-          const bool partial_dense = has_dense && a.block_kind[sched_off + s] == SPLASH_BLOCK_PARTIAL;
+          const bool partial_dense = has_dense && a.block_kind[sched_off + st] == SPLASH_BLOCK_PARTIAL;
           const uint32_t bytes = (has_seg ? L::kSegStage : 0) + (partial_dense ? L::kMaskStage : 0);
-          const int mrow = partial_dense ? a.mask_block[sched_off + s] * kBq : 0;
+          const size_t mblock = partial_dense ? static_cast<size_t>(a.mask_block[sched_off + st]) : 0;
           if (elect_one()) {
             mbar_arrive_expect_tx(SPLASH_BAR(aux_full, slot), bytes);
             if (has_seg)
               bulk_load_1d(seg_u32 + slot * L::kSegStage, a.seg_kv + static_cast<size_t>(b) * a.kv_len + j * BKV,
                            L::kSegStage, SPLASH_BAR(aux_full, slot));
-            if (partial_dense) {
-#pragma unroll
-              for (int t = 0; t < NT; ++t)
-                tma_load_2d(mask_u32 + slot * L::kMaskStage + t * (kTile * BKV), &tm_mask, 0, mrow + t * kTile,
-                            SPLASH_BAR(aux_full, slot));
-            }
+            if (partial_dense)
+              bulk_load_1d(mask_u32 + slot * L::kMaskStage, a.partial_blocks + mblock * L::kMaskStage, L::kMaskStage,
+                           SPLASH_BAR(aux_full, slot));
           }
         }
         if (++slot == stages) { slot = 0; phase ^= 1; }
@@ -283,10 +308,10 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       if (elect_one()) prefetch_tensormap(&tm_v);
       int slot = 0;
       uint32_t phase = 0;
-      int j_next = a.block_list[sched_off];
+      int j_next = a.block_list[sched_off + (step_at(0) & 0x7fffu)];
       for (int s = 0; s < n; ++s) {
         const int kv_row = kv_row0 + j_next * BKV;
-        if (s + 1 < n) j_next = a.block_list[sched_off + s + 1];
+        if (s + 1 < n) j_next = a.block_list[sched_off + (step_at(s + 1) & 0x7fffu)];
         if (s >= stages && !warp_wait(SPLASH_BAR(v_empty, slot), phase ^ 1, ctx, kSiteTmaVEmpty, s)) break;
         if (elect_one()) {
           mbar_arrive_expect_tx(SPLASH_BAR(v_full, slot), L::kVStage);
@@ -461,8 +486,9 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       const int s_first = (AW == 2) ? grp : 0;
       int slot = s_first % stages;
       uint32_t phase = (s_first / stages) & 1;
-      int kind = s_first < n ? a.block_kind[sched_off + s_first] : 0;
-      int jblk = s_first < n ? a.block_list[sched_off + s_first] : 0;
+      uint32_t entry = s_first < n ? step_at(s_first) : 0u;
+      int kind = s_first < n ? a.block_kind[sched_off + (entry & 0x7fffu)] : 0;
+      int jblk = s_first < n ? a.block_list[sched_off + (entry & 0x7fffu)] : 0;
       bool alive = true;
       float sv[BKV];  // the current row of S
       auto load_row = [&](int buf, uint32_t par, int step) {
@@ -476,9 +502,11 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
       for (int s = s_first; s < n; s += AW) {
         const int kind_now = kind, j_now = jblk;
+        const bool seg_compare = has_seg && !(entry & kSegUniformBit);
         if (s + AW < n) {
-          kind = a.block_kind[sched_off + s + AW];
-          jblk = a.block_list[sched_off + s + AW];
+          entry = step_at(s + AW);
+          kind = a.block_kind[sched_off + (entry & 0x7fffu)];
+          jblk = a.block_list[sched_off + (entry & 0x7fffu)];
         }
         const int buf = (NT == 2) ? t : (s & 1);
         const uint32_t par = (NT == 2) ? (s & 1) : ((s >> 1) & 1);
@@ -508,19 +536,21 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           }
         }
         if (partial && has_dense) {
-          const uint32_t mrow = mask_u32 + slot * L::kMaskStage + t * (kTile * BKV);
-#pragma unroll
-          for (int c = 0; c < BKV / 16; ++c) {
-            uint32_t off = row * BKV + c * 16;
-            off ^= ((off >> 7) & (BKV == 128 ? 7u : 3u)) << 4;  // TMA swizzle of the mask tile
-            const uint4 w = lds128(mrow + off);
-            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-            for (int e = 0; e < 16; ++e)
-              if (((ww[e >> 2] >> ((e & 3) * 8)) & 0xff) == 0) sv[c * 16 + e] = -INFINITY;
+          // One bit per element, BKV / 8 bytes per q row, rows of the tile(s) back to back.
+          const uint32_t mrow = mask_u32 + slot * L::kMaskStage + (t * kTile + row) * (BKV / 8);
+          uint32_t bits[BKV / 32];
+          if constexpr (BKV == 128) {
+            const uint4 w = lds128(mrow);
+            bits[0] = w.x; bits[1] = w.y; bits[2] = w.z; bits[3] = w.w;
+          } else {
+            bits[0] = lds32(mrow);
+            bits[1] = lds32(mrow + 4);
           }
+#pragma unroll
+          for (int i = 0; i < BKV; ++i)
+            if (!((bits[i >> 5] >> (i & 31)) & 1u)) sv[i] = -INFINITY;
         }
-        if (has_seg) {
+        if (seg_compare) {
           const uint32_t segs = seg_u32 + slot * L::kSegStage;
 #pragma unroll
           for (int c = 0; c < BKV / 4; ++c) {

@@ -5,6 +5,7 @@
 
 #include <cstdlib>
 
+#include "dispatch.h"
 #include "fwd_kernel.cuh"
 #include "host_common.cuh"
 
@@ -15,7 +16,11 @@ int launch_fwd_plain(const SplashParams& p, cudaStream_t stream) {
   using L = FwdLayout<D, DV, BKV, NT, AW>;
   const bool dense = p.partial_blocks != nullptr;
   const bool seg = p.seg_q != nullptr;
-  const size_t smem = L::smem_bytes(p.num_stages, dense, seg);
+  // The list of steps that survive segment skipping needs max_steps 16-bit entries; without room
+  // for it (or with more than 2^15 steps) every scheduled block is computed.
+  bool skipping = seg && p.seg_ranges != nullptr && p.max_steps < (1 << 15);
+  if (skipping && L::smem_bytes(p.num_stages, dense, seg, p.max_steps) > kMaxDynamicSmem) skipping = false;
+  const size_t smem = L::smem_bytes(p.num_stages, dense, seg, skipping ? p.max_steps : 0);
   if (smem > kMaxDynamicSmem) {
     char d[96];
     snprintf(d, sizeof d, "%zu > %zu bytes; reduce num_stages or block_kv", smem, kMaxDynamicSmem);
@@ -27,19 +32,14 @@ int launch_fwd_plain(const SplashParams& p, cudaStream_t stream) {
   const CUtensorMapDataType dt = tmap_dtype(p.dtype);
   const uint64_t q_rows = static_cast<uint64_t>(p.batch) * p.heads * p.q_len;
   const uint64_t kv_rows = static_cast<uint64_t>(p.batch) * p.kv_heads * p.kv_len;
-  CUtensorMap tm_q, tm_k, tm_v, tm_o, tm_mask;
-  memset(&tm_mask, 0, sizeof tm_mask);
+  CUtensorMap tm_q, tm_k, tm_v, tm_o;
   int rc;
   if ((rc = make_tmap_2d(&tm_q, p.q, dt, 2, q_rows, D, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if ((rc = make_tmap_2d(&tm_k, p.k, dt, 2, kv_rows, D, BKV, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if ((rc = make_tmap_2d(&tm_v, p.v, dt, 2, kv_rows, DV, BKV, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if ((rc = make_tmap_2d(&tm_o, p.out, dt, 2, q_rows, DV, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
-  if (dense) {
-    const uint64_t mrows = static_cast<uint64_t>(p.num_partial_blocks) * p.block_q;
-    if ((rc = make_tmap_2d(&tm_mask, p.partial_blocks, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, mrows, BKV, 128, BKV,
-                           BKV == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B)))
-      return rc;
-  }
+  if (dense && (reinterpret_cast<uintptr_t>(p.partial_blocks) & 15))
+    return fail(SPLASH_INVALID_ARGUMENT, "partial_blocks not 16-byte aligned");
 
   FwdArgs a;
   a.num_steps = p.num_steps;
@@ -50,6 +50,9 @@ int launch_fwd_plain(const SplashParams& p, cudaStream_t stream) {
   a.mask_desc = p.mask_desc;
   a.seg_q = p.seg_q;
   a.seg_kv = p.seg_kv;
+  a.partial_blocks = reinterpret_cast<const uint8_t*>(p.partial_blocks);
+  a.seg_q_ranges = skipping ? seg_q_ranges(p) : nullptr;
+  a.seg_kv_ranges = skipping ? seg_kv_ranges(p) : nullptr;
   a.out = p.out;
   a.lse_out = p.lse_out;
   a.status = p.status;
@@ -71,7 +74,7 @@ int launch_fwd_plain(const SplashParams& p, cudaStream_t stream) {
   auto kernel = splash_fwd_kernel<D, DV, BKV, NT, AW, PLAIN, BF16>;
   if ((rc = opt_in_smem(kernel, smem))) return rc;
   const unsigned grid = static_cast<unsigned>(a.q_blocks) * p.heads * p.batch;
-  kernel<<<grid, L::kThreads, smem, stream>>>(tm_q, tm_k, tm_v, tm_o, tm_mask, a);
+  kernel<<<grid, L::kThreads, smem, stream>>>(tm_q, tm_k, tm_v, tm_o, a);
   SPLASH_CUDA_CHECK(cudaGetLastError());
   return SPLASH_OK;
 }

@@ -37,6 +37,7 @@ EXPORTED_SYMBOLS = (
     "splash_bwd_fused",
     "splash_bwd_fused_workspace_bytes",
     "splash_bwd_fused_static",
+    "splash_seg_ranges_bytes",
     "splash_read_status",
     "splash_status_string",
     "splash_last_error",
@@ -66,6 +67,7 @@ class SplashParams(Structure):
       ("block_q", c_int32), ("block_kv", c_int32),
       ("num_stages", c_int32), ("sub_block", c_int32),
       ("mask_value", c_float), ("soft_cap", c_float),
+      ("seg_ranges", c_void_p),
   ]
 
 
@@ -96,6 +98,9 @@ def load():
     lib.splash_bwd_delta.argtypes = [c_void_p, c_void_p, c_void_p, c_int64,
                                      c_int32, c_int32, c_void_p]
     lib.splash_bwd_delta.restype = c_int
+  if hasattr(lib, "splash_seg_ranges_bytes"):
+    lib.splash_seg_ranges_bytes.argtypes = [POINTER(SplashParams)]
+    lib.splash_seg_ranges_bytes.restype = c_int64
   if hasattr(lib, "splash_bwd_fused_workspace_bytes"):
     lib.splash_bwd_fused_workspace_bytes.argtypes = [POINTER(SplashParams)]
     lib.splash_bwd_fused_workspace_bytes.restype = c_int64

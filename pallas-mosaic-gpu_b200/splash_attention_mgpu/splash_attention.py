@@ -135,6 +135,16 @@ def _upload(x, device):
   return torch.from_numpy(np.ascontiguousarray(x)).to(device)
 
 
+def _upload_packed(blocks, device):
+  """Dense partial blocks [n, rows, cols] (1 = attend) -> device bytes [n, rows, cols / 8], one bit
+  per element, bit i of byte j standing for column 8 * j + i.  The kernels stream these instead of
+  the int8 blocks: an eighth of the bytes per partial block and per CTA ring slot."""
+  if blocks is None:
+    return None
+  packed = np.packbits(np.asarray(blocks).astype(bool), axis=-1, bitorder="little")
+  return torch.from_numpy(np.ascontiguousarray(packed)).to(device)
+
+
 def _row_schedule(info: mask_info_lib.GpuMaskInfo, device) -> _DeviceSchedule:
   has_partial = bool((info.block_kind == mask_info_lib.PARTIAL).any())
   dense = info.partial_mask_blocks is not None
@@ -144,7 +154,7 @@ def _row_schedule(info: mask_info_lib.GpuMaskInfo, device) -> _DeviceSchedule:
       block_list=_upload(info.kv_block, device),
       block_kind=_upload(info.block_kind, device),
       mask_block=_upload(info.mask_block, device) if dense else None,
-      partial_blocks=_upload(info.partial_mask_blocks, device) if dense else None,
+      partial_blocks=_upload_packed(info.partial_mask_blocks, device) if dense else None,
       mask_desc=(_upload(info.mask_descriptors, device)
                  if (not dense and info.mask_descriptors is not None) else None),
       mask_heads=info.num_steps.shape[0],
@@ -163,7 +173,7 @@ def _column_schedule(info: mask_info_lib.GpuMaskInfo, device) -> _DeviceSchedule
       block_list=_upload(info.dkv_q_block, device),
       block_kind=_upload(info.dkv_block_kind, device),
       mask_block=_upload(info.dkv_mask_block, device) if dense else None,
-      partial_blocks=_upload(info.partial_mask_blocks_t, device) if dense else None,
+      partial_blocks=_upload_packed(info.partial_mask_blocks_t, device) if dense else None,
       mask_desc=(_upload(info.mask_descriptors, device)
                  if (not dense and info.mask_descriptors is not None) else None),
       mask_heads=info.dkv_num_steps.shape[0],
@@ -442,6 +452,14 @@ def _base_params(kernel: SplashAttentionKernel, q, k, v, segment_ids,
   p.mask_value = kernel.mask_value
   cap = kernel.attn_logits_soft_cap
   p.soft_cap = 0.0 if cap is None else float(cap)
+  if segment_ids is not None and os.environ.get("SPLASH_SEG_SKIP", "1") == "1":
+    # Scratch for segment-aware block skipping: the entry point fills it and the kernels leave out
+    # blocks whose q and kv segment ids cannot meet.  (Freed after the launch; the caching allocator
+    # reuses it only behind the kernels on this stream.)
+    nbytes = int(_ffi.load().splash_seg_ranges_bytes(ctypes.byref(p)))
+    if nbytes > 0:
+      p._seg_ranges = torch.empty(nbytes // 4, dtype=torch.int32, device=q.device)
+      p.seg_ranges = p._seg_ranges.data_ptr()
   return p
 
 
