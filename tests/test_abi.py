@@ -38,8 +38,9 @@ def test_params_struct_mirrors_the_header():
     names[0] = names[0].split()[-1].lstrip("*")
     fields.extend(names)
   assert fields == [name for name, _ in _ffi.SplashParams._fields_]
-  # 22 pointers, 15 int32, 2 floats, padded to pointer alignment.
-  assert ctypes.sizeof(_ffi.SplashParams) == 22 * 8 + 15 * 4 + 2 * 4 + 4
+  # 22 pointers, 15 int32, 2 floats, padding to pointer alignment, then the appended scratch pointer.
+  assert ctypes.sizeof(_ffi.SplashParams) == 22 * 8 + 15 * 4 + 2 * 4 + 4 + 8
+  assert _ffi.SplashParams.seg_ranges.offset == 248
 
 
 def test_status_strings_and_argument_checks_need_no_gpu():
