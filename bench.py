@@ -533,6 +533,8 @@ def run_ours(args):
       bwd = float(np.mean([e[1].elapsed_time(e[2]) for e in ev]))
     return ms, fwd, bwd, (first, sampler.mark())
 
+  for _ in range(3):   # eager warm-up again: the capture above changed the allocator's state
+    step()
   eager_ms, fwd_ms, bwd_ms, eager_marks = timed_loop(args.steps, False, split=True)
   if wl.forward_only:
     fwd_ms = eager_ms / args.steps

@@ -58,8 +58,13 @@ _UNIT_BYTES = {"byte": 1.0, "Kbyte": 1e3, "Mbyte": 1e6, "Gbyte": 1e9, "Tbyte": 1
 
 
 def read_report(path: str, launch: int = 0) -> dict[str, tuple[str, str]]:
-  """{metric: (unit, value)} of one captured launch of an .ncu-rep file."""
-  out = subprocess.run(["ncu", "-i", path, "--page", "raw", "--csv"], capture_output=True, text=True, check=True).stdout
+  """{metric: (unit, value)} of one captured launch of an .ncu-rep file, or of the CSV that
+  `ncu -i REPORT --page raw --csv` printed for it."""
+  if path.endswith(".csv"):
+    with open(path) as f:
+      out = f.read()
+  else:
+    out = subprocess.run(["ncu", "-i", path, "--page", "raw", "--csv"], capture_output=True, text=True, check=True).stdout
   rows = list(csv.reader(out.splitlines()))
   header, units, values = rows[0], rows[1], rows[2 + launch]
   return {h: (u, v) for h, u, v in zip(header, units, values)}
