@@ -193,8 +193,11 @@ const char* splash_last_error(void);
  *           3 = no GEMM: the kernel waits on a barrier nothing arrives on, so that its
  *               bounded wait runs out (about a second); it then unwinds and leaves
  *               {1, 102, 0, 7} in `status`.  Checks the report path without a fault.
+ *           4 = A in shared memory, K-major, unswizzled 8 x 8 core matrices written by
+ *               the kernel's own threads (global A is [128, kd] row-major)
  *   b_mode: 0 = K-major (global B is [n, kd] row-major)
  *           1 = N-major (global B is [kd, n] row-major)
+ *           2 = K-major, unswizzled core matrices (global B is [n, kd] row-major)
  * No counterpart in the reference; it exists for the test-suite. */
 int splash_selftest_umma(const void* a, const void* b, float* d, int32_t n, int32_t kd, int32_t a_mode,
                          int32_t b_mode, int32_t dtype, int32_t* status, void* stream);

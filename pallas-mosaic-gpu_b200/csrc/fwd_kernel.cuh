@@ -41,6 +41,12 @@
 #include "ptx.cuh"
 #include "seg_skip.cuh"
 
+// Timeline marks for debugging builds; empty in the product.
+#ifndef SPLASH_TRACE_MARK
+#define SPLASH_TRACE_MARK(role, t, k)
+#define SPLASH_TRACE_NS(role, t, k)
+#endif
+
 namespace splash {
 
 constexpr float kLog2e = 1.4426950408889634f;
@@ -374,17 +380,23 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           for (int s = 0; s < n && ok; ++s) {
             const int cur = s & 1;
             const uint32_t par = (s >> 1) & 1;
+            SPLASH_TRACE_MARK(0, s, 0);
             if (s + 2 < n) {
               if (!warp_wait(SPLASH_BAR(k_full, ks), kp, ctx, kSiteMmaK, s + 2)) break;
+              SPLASH_TRACE_MARK(0, s, 1);
               if (!warp_wait(SPLASH_BAR(s_free, cur), par, ctx, kSiteMmaSFree, s)) break;
+              SPLASH_TRACE_MARK(0, s, 2);
               tc_fence_after();
               issue_qk(0, ks, tmem + cur * BKV);
               umma_commit_w(SPLASH_BAR(s_ready, cur));
               umma_commit_w(SPLASH_BAR(k_empty, ks));
               if (++ks == stages) { ks = 0; kp ^= 1; }
             }
+            SPLASH_TRACE_MARK(0, s, 3);
             if (!warp_wait(SPLASH_BAR(v_full, slot), phase, ctx, kSiteMmaV, s)) break;
+            SPLASH_TRACE_MARK(0, s, 4);
             if (!warp_wait(SPLASH_BAR(p_ready, cur), par, ctx, kSiteMmaP, s)) break;
+            SPLASH_TRACE_MARK(0, s, 5);
             tc_fence_after();
             issue_pv(0, slot, tmem + L::kPCol + cur * L::kPStride, s > 0);
             umma_commit_w(SPLASH_BAR(v_empty, slot));
@@ -511,8 +523,10 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const int buf = (NT == 2) ? t : (s & 1);
         const uint32_t par = (NT == 2) ? (s & 1) : ((s >> 1) & 1);
         const uint32_t p_tmem = tmem_row + L::kPCol + buf * L::kPStride;
+        if ((warp & 3) == 0) { SPLASH_TRACE_MARK(1 + grp, s, 0); SPLASH_TRACE_NS(1 + grp, s, 7); }
         if (!load_row(buf, par, s)) { alive = false; break; }
         tmem_wait_ld();
+        if ((warp & 3) == 0) SPLASH_TRACE_MARK(1 + grp, s, 1);
         if constexpr (AW == 2) {
           // The row is in registers: the tensor core may write the scores of step s + 2.
           tc_fence_before();
@@ -593,6 +607,7 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             }
           }
         }
+        if ((warp & 3) == 0) SPLASH_TRACE_MARK(1 + grp, s, 2);
         const float m_new = fmaxf(m_run, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
         const bool moved = (m_new - m_run) * kLog2e > kRescaleThreshold;  // false for NaN (-inf - -inf)
         float alpha = 1.f;
@@ -609,6 +624,7 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           // P has its own columns: they are free once P.V of this group's previous step is done.
           if (s >= 2 && !warp_wait(SPLASH_BAR(pv_done, s & 1), ((s - 2) >> 1) & 1, ctx, kSiteSmxPv, s)) { alive = false; break; }
         }
+        if ((warp & 3) == 0) SPLASH_TRACE_MARK(1 + grp, s, 3);
         const float m_scaled = (m_run == -INFINITY) ? 0.f : m_run * kLog2e;
         const float2 scale2 = make_float2(kLog2e, kLog2e), shift2 = make_float2(-m_scaled, -m_scaled);
         float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
@@ -629,6 +645,7 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           tmem_st16(p_tmem + c * 16, pk);
         }
         l_run += (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
+        if ((warp & 3) == 0) SPLASH_TRACE_MARK(1 + grp, s, 4);
 
         // O may only be touched once P.V of the previous step has finished.  With two
         // tiles the s_ready wait above already certifies that (the tensor core runs
@@ -653,6 +670,7 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(SPLASH_BAR(p_ready, buf));
+        if ((warp & 3) == 0) SPLASH_TRACE_MARK(1 + grp, s, 5);
 #pragma unroll
         for (int i = 0; i < AW; ++i)
           if (++slot == stages) { slot = 0; phase ^= 1; }

@@ -396,6 +396,21 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t 
   return (static_cast<uint64_t>(hi) << 32) | lo;
 }
 
+// Shared-memory matrix descriptor for an unswizzled K-major operand stored as 8 x 8
+// "core matrices" (8 rows of 16 bytes, 128 contiguous bytes each): LBO = bytes from one
+// core matrix to the next along K, SBO = bytes from one group of 8 rows to the next.
+// A K = 16 slice is two core matrices; step along K by adding 2 * LBO to the start.
+__device__ __forceinline__ uint32_t desc_lo_plain(uint32_t smem_addr, uint32_t lbo_bytes) {
+  return ((smem_addr & 0x3ffff) >> 4) | (((lbo_bytes >> 4) & 0x3fff) << 16);
+}
+__host__ __device__ constexpr uint32_t desc_hi_plain(uint32_t sbo_bytes) {
+  return ((sbo_bytes >> 4) & 0x3fff) | (1u << 14);
+}
+// Byte offset of element (row, k) in such a tile with `kd` elements of K per row.
+__host__ __device__ constexpr uint32_t core_matrix_offset(uint32_t row, uint32_t k, uint32_t kd) {
+  return (row >> 3) * (kd >> 3) * 128u + (k >> 3) * 128u + (row & 7u) * 16u + (k & 7u) * 2u;
+}
+
 // ---------------------------------------------------------------------------
 // tcgen05.ld / st, shape 32x32b: lane i of the warp owns TMEM lane (base + i) and
 // receives N consecutive 32-bit columns.  A warp may only touch the 32 lanes of

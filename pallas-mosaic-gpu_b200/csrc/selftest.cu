@@ -16,7 +16,7 @@ struct SelftestBars {
 
 __global__ void __launch_bounds__(128, 1)
 selftest_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                     const void* a_gmem, float* d_gmem, int n, int kd, int a_mode, int b_mode, int bf16,
+                     const void* a_gmem, const void* b_gmem, float* d_gmem, int n, int kd, int a_mode, int b_mode, int bf16,
                      int32_t* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -58,6 +58,18 @@ selftest_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
     }
     tmem_wait_st();
   }
+  if (a_mode == 4) {
+    // Unswizzled core-matrix layout, written by the threads themselves.
+    const uint16_t* arow = static_cast<const uint16_t*>(a_gmem) + static_cast<size_t>(row) * kd;
+    for (int k = 0; k < kd; ++k) *reinterpret_cast<uint16_t*>(a_smem + core_matrix_offset(row, k, kd)) = arow[k];
+  }
+  if (b_mode == 2) {
+    for (int r = row; r < n; r += 128) {
+      const uint16_t* brow = static_cast<const uint16_t*>(b_gmem) + static_cast<size_t>(r) * kd;
+      for (int k = 0; k < kd; ++k) *reinterpret_cast<uint16_t*>(b_smem + core_matrix_offset(r, k, kd)) = brow[k];
+    }
+  }
+  if (a_mode == 4 || b_mode == 2) fence_proxy_async_smem();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -67,9 +79,9 @@ selftest_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
     // out (about a second), records site 102 / step 7 and the kernel unwinds normally.
     if (warp == 0) warp_wait(smem_u32(&bars->full), 0, ctx, 102, 7);
   } else if (threadIdx.x == 0) {
-    uint32_t bytes = n * kd * 2 + (a_mode == 2 ? 0 : 128 * kd * 2);
+    uint32_t bytes = (b_mode == 2 ? 0 : n * kd * 2) + ((a_mode == 2 || a_mode == 4) ? 0 : 128 * kd * 2);
     const uint32_t full = smem_u32(&bars->full);
-    mbar_arrive_expect_tx(full, bytes);
+    if (bytes > 0) mbar_arrive_expect_tx(full, bytes);
     if (a_mode == 0) {
       for (int c = 0; c < kd / 64; ++c) tma_load_2d(smem_u32(a_smem) + c * (128 * 128), &tm_a, c * 64, 0, full);
     } else if (a_mode == 1) {
@@ -77,27 +89,33 @@ selftest_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
     }
     if (b_mode == 0) {
       for (int c = 0; c < kd / 64; ++c) tma_load_2d(smem_u32(b_smem) + c * (n * 128), &tm_b, c * 64, 0, full);
-    } else {
+    } else if (b_mode == 1) {
       for (int c = 0; c < n / 64; ++c) tma_load_2d(smem_u32(b_smem) + c * (kd * 128), &tm_b, c * 64, 0, full);
     }
+    if (bytes == 0) mbar_arrive(full);
     if (mbar_wait(full, 0, ctx, 100, 0)) {
       tc_fence_after();
       const uint32_t idesc = make_idesc(bf16 != 0, 128, n, a_mode == 1, b_mode == 1);
       const uint32_t a_addr = smem_u32(a_smem), b_addr = smem_u32(b_smem);
       for (int kk = 0; kk < kd / 16; ++kk) {
+        const uint32_t plain_hi = desc_hi_plain((kd / 8) * 128);
         uint64_t bdesc;
         if (b_mode == 0)
           bdesc = make_smem_desc(b_addr + (kk / 4) * (n * 128) + (kk % 4) * 32, 16, 1024);
-        else
+        else if (b_mode == 1)
           bdesc = make_smem_desc(b_addr + kk * 2048, kd * 128, 1024);
+        else
+          bdesc = (static_cast<uint64_t>(plain_hi) << 32) | desc_lo_plain(b_addr + kk * 256, 128);
         if (a_mode == 2) {
           umma_ts(tmem, tmem + a_tmem_col + kk * 8, bdesc, idesc, kk > 0);
         } else {
           uint64_t adesc;
           if (a_mode == 0)
             adesc = make_smem_desc(a_addr + (kk / 4) * (128 * 128) + (kk % 4) * 32, 16, 1024);
-          else
+          else if (a_mode == 1)
             adesc = make_smem_desc(a_addr + kk * 2048, kd * 128, 1024);
+          else
+            adesc = (static_cast<uint64_t>(plain_hi) << 32) | desc_lo_plain(a_addr + kk * 256, 128);
           umma_ss(tmem, adesc, bdesc, idesc, kk > 0);
         }
       }
@@ -132,7 +150,7 @@ extern "C" int splash_selftest_umma(const void* a, const void* b, float* d, int3
   using namespace splash;
   if (!a || !b || !d || !status) return fail(SPLASH_INVALID_ARGUMENT, "null pointer");
   if (n % 64 || n < 64 || n > 256 || kd % 64 || kd < 64 || kd > 256) return fail(SPLASH_INVALID_ARGUMENT, "n, kd must be multiples of 64 in [64, 256]");
-  if (a_mode < 0 || a_mode > 3 || b_mode < 0 || b_mode > 1) return fail(SPLASH_INVALID_ARGUMENT, "bad operand mode");
+  if (a_mode < 0 || a_mode > 4 || b_mode < 0 || b_mode > 2) return fail(SPLASH_INVALID_ARGUMENT, "bad operand mode");
   const CUtensorMapDataType dt = tmap_dtype(dtype);
   CUtensorMap tm_a, tm_b;
   int rc;
@@ -145,7 +163,7 @@ extern "C" int splash_selftest_umma(const void* a, const void* b, float* d, int3
   const size_t smem = 193 * 1024 + 1024;
   if ((rc = opt_in_smem(selftest_umma_kernel, smem))) return rc;
   selftest_umma_kernel<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(
-      tm_a, tm_b, a, d, n, kd, a_mode, b_mode, dtype == SPLASH_DTYPE_BF16, status);
+      tm_a, tm_b, a, b, d, n, kd, a_mode, b_mode, dtype == SPLASH_DTYPE_BF16, status);
   SPLASH_CUDA_CHECK(cudaGetLastError());
   return SPLASH_OK;
 }

@@ -583,8 +583,10 @@ def _backward(kernel: SplashAttentionKernel, bs: BlockSizes, q, k, v,
       _ffi.check(lib.splash_bwd_dq(ctypes.byref(p), stream),
                  "splash attention dQ")
       p = params(cols)
+      # The dK/dV kernel always works in 64-row steps; `block_q_dkv` is accepted for compatibility
+      # with the reference's BlockSizes, and the budgets are checked for the tiling that runs.
       p.sub_block = pick(
-          bs.block_q_dkv,
+          64,
           lambda sb: cfg.bwd_dkv_tmem_cols(head_dim, head_dim_v, sb),
           lambda sb: cfg.bwd_dkv_smem_bytes(head_dim=head_dim, head_dim_v=head_dim_v,
                                             sub_block=sb, **common),

@@ -142,8 +142,8 @@ WIDE_CASES = [
     dict(mask_name="dense", d=64, segs=True),
     dict(mask_name="causal", d=64, dv=128),
     dict(mask_name="causal", d=128, dv=64),
-    # Many more tiles than SMs, most of them one to four steps long: every CTA of the
-    # persistent kernel walks several tiles, one-step tiles back to back included.
+    # Many more tiles than SMs, most of them one to four steps long: several waves of short
+    # CTAs, one-step tiles included.
     dict(mask_name="causal", d=128, s=512, b=4, h=40),
     dict(mask_name="local", d=64, s=1024, b=3, h=24, segs=True),
     dict(mask_name="chunked", d=128, s=1024, b=2, h=32, kvh=8, cap=5.0),

@@ -13,7 +13,7 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("a_mode,b_mode", [(0, 0), (2, 1), (0, 1), (1, 0), (1, 1), (2, 0)])
+@pytest.mark.parametrize("a_mode,b_mode", [(0, 0), (2, 1), (0, 1), (1, 0), (1, 1), (2, 0), (4, 2), (0, 2), (4, 0)])
 @pytest.mark.parametrize("n,kd", [(128, 128), (64, 64), (256, 64), (64, 256), (128, 192)])
 def test_umma_selftest(a_mode, b_mode, n, kd, dtype):
   lib = _ffi.load()
