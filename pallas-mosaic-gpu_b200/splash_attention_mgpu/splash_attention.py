@@ -245,8 +245,21 @@ class SplashAttentionKernel:
     with a two-stage ring, which leaves room for two CTAs per SM and suits
     short rows (local windows, short sequences), and 128-wide blocks with two
     softmax warpgroups alternating over the KV steps for long rows.  The
-    two-tile kernel (block_q=256) runs when asked for.
+    two-tile kernel (block_q=256) runs when asked for, and at head_dim 64 on masks
+    whose 256-row schedule costs nothing extra.
     """
+    if head_dim == head_dim_v == 64:
+      # Measured at seq 8192 (tuning.py): 64-wide KV blocks with a two-stage ring (two CTAs per SM)
+      # lead on causal-like masks; the two-tile kernel leads where its 256-row schedule visits no
+      # extra blocks (full masks).  With segment ids every tiling is within 2 % of the others.
+      extra = self.pingpong_extra_work
+      pp = dict(head_dim=head_dim, block_kv=128, num_stages=2, itemsize=itemsize,
+                has_dense_mask=self.fwd_info(128, 128).partial_mask_blocks is not None,
+                has_segments=has_segments, save_residuals=save_residuals)
+      if (extra is not None and extra <= 1.005 and not has_segments
+          and cfg.pingpong_smem_bytes(**pp) <= cfg.SMEM_BYTES):
+        return 256, 128, 2
+      return 128, 64, 2
     if head_dim != head_dim_v or head_dim != 128:
       bkv, stages = auto_forward_tiles(head_dim, 128)
       return 128, bkv, stages

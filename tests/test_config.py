@@ -33,8 +33,10 @@ def test_auto_forward_tiling_by_row_length():
   assert tiles(sa.CausalMask((2048, 2048)), 128) == (128, 64, 2)
   assert tiles(sa.LocalMask((s, s), (1024, 0), 0), 128) == (128, 64, 2)
   assert tiles(sa.ChunkedCausalMask((s, s), 1024), 128) == (128, 64, 2)
+  # Head dim 64: two CTAs per SM with 64-wide blocks; the two-tile kernel where its schedule is free.
+  assert tiles(sa.CausalMask((s, s)), 64) == (128, 64, 2)
+  assert tiles(sa.FullMask((s, s)), 64) == (256, 128, 2)
   # Other head dims keep the one-tile defaults.
-  assert tiles(sa.FullMask((s, s)), 64) == (128, 64, 3)
   assert tiles(sa.FullMask((s, s)), 256) == (128, 128, 2)
   # The two-tile kernel runs when asked for; open fields are filled in around it.
   k = sa.make_splash_mha(sa.FullMask((s, s)), block_sizes=sa.BlockSizes(block_q=256))
@@ -63,7 +65,7 @@ def test_resolved_tiles_of_the_benchmark_configs():
   assert (bs.block_q, bs.block_kv, bs.num_stages) == (128, 64, 2)
   k = sa.make_splash_mha(sa.FullMask((8192, 8192)))
   bs = k.resolved_block_sizes(64, 64, has_segments=True)
-  assert (bs.block_q, bs.block_kv, bs.num_stages) == (128, 64, 3)
+  assert (bs.block_q, bs.block_kv, bs.num_stages) == (128, 64, 2)
 
 
 def test_numpy_masks_become_multi_head_masks():

@@ -140,7 +140,7 @@ def test_packed_documents_f16_d64_forward_backward(variant):
     kernel = sa.make_splash_mha(sa.MultiHeadMask(masks))
     assert kernel.info.num_steps.shape[0] == heads and kernel.info.partial_mask_blocks is None
   bs = kernel.resolved_block_sizes(d, d, has_segments=True)
-  assert (bs.block_q, bs.block_kv, bs.num_stages) == (128, 64, 3)
+  assert (bs.block_q, bs.block_kv, bs.num_stages) == (128, 64, 2)
   out, (lse,) = kernel(q, k, v, seg, save_residuals=True)
   sa.check_device_status()
   rows = np.sort(np.random.default_rng(2).choice(s, 160, replace=False))
