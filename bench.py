@@ -535,9 +535,25 @@ def run_ours(args):
 
   for _ in range(3):   # eager warm-up again: the capture above changed the allocator's state
     step()
-  eager_ms, fwd_ms, bwd_ms, eager_marks = timed_loop(args.steps, False, split=True)
-  if wl.forward_only:
-    fwd_ms = eager_ms / args.steps
+  eager_ms, fwd_in_step_ms, bwd_ms, eager_marks = timed_loop(args.steps, False, split=True)
+  # The forward on its own, as the reference's benchmark times it (tools/bench.py:70-76: the forward
+  # with its logsumexp residual in a loop of its own, then forward + backward).
+  fwd_ms = eager_ms / args.steps
+  if not wl.forward_only and n_local:
+    qd, kd, vd = q.detach(), k.detach(), v.detach()
+    for _ in range(3):
+      kernel(qd, kd, vd, seg, save_residuals=True)
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for _ in range(args.steps):
+      kernel(qd, kd, vd, seg, save_residuals=True)
+    f1.record()
+    barrier()
+    fwd_ms = f0.elapsed_time(f1) / args.steps
+  elif not wl.forward_only:
+    barrier()
+    barrier()
   graph_ms, _, _, graph_marks = timed_loop(args.steps, True) if graph is not None else (float("nan"), 0, 0, eager_marks)
   sa.check_device_status()
 
@@ -632,13 +648,14 @@ def run_ours(args):
       check = dict(gathered_units=int(units.shape[0]), recomputed_on_rank0=n_checked, bit_identical=same,
                    how="NCCL all_gather of the forward outputs, then one unit per rank recomputed on rank 0")
 
-  stats = [eager_ms, graph_ms if graph is not None else -1.0, e2e_ms, fwd_ms, bwd_ms, sus_ms]
+  stats = [eager_ms, graph_ms if graph is not None else -1.0, e2e_ms, fwd_ms, bwd_ms, sus_ms,
+           fwd_in_step_ms if fwd_in_step_ms == fwd_in_step_ms else -1.0]
   times = torch.tensor(stats, dtype=torch.float64, device=dev)
   sums = torch.tensor([float(h2d_local), float(d2h_local), local_fwd_flops], dtype=torch.float64, device=dev)
   if dist is not None:
     dist.all_reduce(times, op=dist.ReduceOp.MAX)
     dist.all_reduce(sums, op=dist.ReduceOp.SUM)
-  eager_ms, graph_ms, e2e_ms, fwd_ms, bwd_ms, sus_ms = times.tolist()
+  eager_ms, graph_ms, e2e_ms, fwd_ms, bwd_ms, sus_ms, fwd_in_step_ms = times.tolist()
   h2d, d2h, fwd_flops_sum = sums.tolist()
   assert abs(fwd_flops_sum - fwd_flops) <= 1e-6 * fwd_flops, "the ranks' units do not add up to the workload"
 
@@ -738,7 +755,8 @@ def run_ours(args):
                      per_rank=f"rank r runs units [r*{part.num_units}//{world} ...): {n_local} of {part.num_units} on rank 0",
                      eager_ms_per_step=eager_ms / args.steps,
                      graph_ms_per_step=graph_ms / args.steps if graph_ms > 0 else None, graph_error=graph_error),
-        fwd_tflops=fwd_tflops, fwd_ms=fwd_ms, bwd_ms=None if wl.forward_only else bwd_ms, fwd256_tflops=fwd256,
+        fwd_tflops=fwd_tflops, fwd_ms=fwd_ms, bwd_ms=None if wl.forward_only else bwd_ms,
+        fwd_ms_inside_step=None if wl.forward_only else fwd_in_step_ms, fwd256_tflops=fwd256,
         roofline=roofline, roofline_fwd=roofline_fwd, sustained=sus, cpu_baseline=cpu, sdpa=sdpa, check=check,
         e2e=dict(value=fb_flops / (e2e_ms / args.steps * 1e-3) / 1e12, unit=UNIT,
                  h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h, ms_per_step=e2e_ms / args.steps),
