@@ -76,3 +76,39 @@ def test_skipping_changes_nothing(kind, d, h, kvh, mask_name, bs, monkeypatch):
   for name, g, r in zip("qkv", with_skip[1:], ref):
     g = g.float().cpu().numpy()
     assert np.abs(g - r).max() / np.abs(r).max() < 2e-2, name
+
+
+@pytest.mark.parametrize("d,bs", [(128, sa.BlockSizes()), (64, sa.BlockSizes()), (128, sa.BlockSizes(block_q=256))])
+def test_q_blocks_whose_every_step_is_skipped(d, bs, monkeypatch):
+  """q rows whose segment id no key carries: every scheduled step of their CTAs is skipped.
+  They return zeros with lse = mask_value and take no part in the gradients; KV blocks that
+  no surviving q row looks at get zero dK/dV."""
+  s, h = 1024, 2
+  kernel = sa.make_splash_mha(sa.FullMask((s, s)), block_sizes=bs)
+  q, k, v = inputs(1, h, h, s, d, d, torch.bfloat16, False, seed=6, device=DEV, scale=d ** -0.5)
+  do = torch.randn(q.shape, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16).to(DEV)
+  seg_q = np.zeros((1, s), np.int32)
+  seg_q[:, s // 2:] = 7                      # no key has id 7
+  seg_kv = np.zeros((1, s), np.int32)
+  seg_kv[:, 3 * s // 4:] = 9                 # keys no q row can see
+  seg = sa.SegmentIds(torch.from_numpy(seg_q).to(DEV), torch.from_numpy(seg_kv).to(DEV))
+  monkeypatch.setenv("SPLASH_SEG_SKIP", "1")
+  out, (lse,) = kernel(q, k, v, seg, save_residuals=True)
+  qg, kg, vg = (x.clone().requires_grad_(True) for x in (q, k, v))
+  kernel(qg, kg, vg, seg).backward(do)
+  torch.cuda.synchronize()
+  sa.check_device_status()
+  assert torch.all(out[:, :, s // 2:] == 0)
+  assert torch.all(lse[:, :, s // 2:] == kernel.mask_value)
+  assert torch.all(qg.grad[:, :, s // 2:] == 0)
+  assert torch.all(kg.grad[:, :, 3 * s // 4:] == 0) and torch.all(vg.grad[:, :, 3 * s // 4:] == 0)
+  dense = np.ones((1, s, s), bool)
+  ref_out, ref_lse = oracle.attention_forward(dense, q, k, v, (seg_q, seg_kv))
+  ref = oracle.attention_backward(dense, q, k, v, do, (seg_q, seg_kv))
+  live = slice(0, s // 2)
+  np.testing.assert_allclose(out[0, :, live].float().cpu().numpy(), ref_out[0, :, live], atol=2e-2, rtol=2e-2)
+  np.testing.assert_allclose(lse[0, :, live].cpu().numpy(), ref_lse[0, :, live], atol=1e-3, rtol=1e-3)
+  # The oracle spreads rows that see nothing uniformly over all keys; those rows are implementation-defined
+  # (reference tools/fuzz.py:116-124), so gradients are compared where only live rows contribute.
+  got_dq = qg.grad[0, :, live].float().cpu().numpy()
+  assert np.abs(got_dq - ref[0][0, :, live]).max() / np.abs(ref[0][0, :, live]).max() < 2e-2
