@@ -143,7 +143,9 @@ int splash_bwd_dkv(const SplashParams* p, void* stream);
  * splash_attention_mgpu/splash_attention.py:289-290). */
 int splash_bwd_fused(const SplashParams* p, void* stream);
 
-/* Bytes of `dq_acc` scratch splash_bwd_fused needs for these shapes. */
+/* Bytes of `dq_acc` scratch splash_bwd_fused needs for these shapes: the f32 accumulator
+ * batch * heads * q_len * head_dim * 4, and at head_dim 64 another 32 bytes per q row behind it
+ * (lse and delta split into 16-bit parts, operands of the 128-row kernel). */
 int64_t splash_bwd_fused_workspace_bytes(const SplashParams* p);
 
 /* Size of the scratch built into the library for splash_bwd_fused_static. */
@@ -161,8 +163,8 @@ int64_t splash_bwd_fused_workspace_bytes(const SplashParams* p);
  *
  * The dQ accumulator is a fixed SPLASH_STATIC_DQ_ACC_BYTES (16 MiB) array inside the
  * library image; every GPU that loads the library carries it until the process exits.
- * `p->dq_acc` is ignored; all other fields are as for splash_bwd_fused.  Shapes with
- * batch * heads * q_len * head_dim * 4 > SPLASH_STATIC_DQ_ACC_BYTES are refused with
+ * `p->dq_acc` is ignored; all other fields are as for splash_bwd_fused.  Shapes whose
+ * splash_bwd_fused_workspace_bytes() exceeds SPLASH_STATIC_DQ_ACC_BYTES are refused with
  * SPLASH_BUDGET_EXCEEDED.  The call performs no cudaMalloc / cudaFree and no allocating
  * library call.  The first call on each device looks up the array's device address
  * (cudaGetSymbolAddress); make that first call outside any stream capture.  The address

@@ -137,9 +137,15 @@ extern "C" int splash_bwd_dkv(const SplashParams* p, void* stream) {
   return p->head_dim_v == 128 ? launch_bwd_col<128, 128, false>(*p, st) : launch_bwd_col<128, 64, false>(*p, st);
 }
 
+// The f32 dQ accumulator alone.
+static int64_t dq_acc_bytes(const SplashParams* p) {
+  return static_cast<int64_t>(p->batch) * p->heads * p->q_len * p->head_dim * 4;
+}
+
 extern "C" int64_t splash_bwd_fused_workspace_bytes(const SplashParams* p) {
   if (!p) return 0;
-  return static_cast<int64_t>(p->batch) * p->heads * p->q_len * p->head_dim * 4;
+  // Accumulator; at head_dim 64 also 32 bytes per q row for the folded lse / delta operands.
+  return dq_acc_bytes(p) + fold_operand_bytes(*p);
 }
 
 extern "C" int splash_bwd_fused(const SplashParams* p, void* stream) {
@@ -154,7 +160,7 @@ extern "C" int splash_bwd_fused(const SplashParams* p, void* stream) {
                               p->head_dim_v, p->dtype, st, p->dq_acc, p->head_dim))
       return rc;
   } else {
-    SPLASH_CUDA_CHECK(cudaMemsetAsync(p->dq_acc, 0, static_cast<size_t>(splash_bwd_fused_workspace_bytes(p)), st));
+    SPLASH_CUDA_CHECK(cudaMemsetAsync(p->dq_acc, 0, static_cast<size_t>(dq_acc_bytes(p)), st));
   }
   // Head dim 128 takes the kernel that works on whole 128-row q blocks; streamed mask blocks
   // and head dim 64 take the 64-row one.  SPLASH_BWD_WIDE=0 forces the latter (experiments).
@@ -202,7 +208,7 @@ extern "C" int splash_bwd_fused_static(const SplashParams* p, void* stream) {
   const int64_t need = splash_bwd_fused_workspace_bytes(&q);
   if (need <= 0 || static_cast<uint64_t>(need) > kStaticDqAccBytes) {
     char d[160];
-    snprintf(d, sizeof d, "batch * heads * q_len * head_dim * 4 = %lld bytes, the built-in scratch holds %zu",
+    snprintf(d, sizeof d, "the scratch for these shapes is %lld bytes, the built-in one holds %zu",
              static_cast<long long>(need), kStaticDqAccBytes);
     return fail(SPLASH_BUDGET_EXCEEDED, "problem too large for splash_bwd_fused_static", d);
   }

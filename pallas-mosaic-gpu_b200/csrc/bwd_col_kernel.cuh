@@ -53,6 +53,8 @@ struct BwdArgs {
   const int2* seg_kv_ranges;  // [batch, kv_len / 64]
   const float* lse;
   const float* delta;
+  const uint8_t* aux_lse;    // 128-row fused kernel at head_dim 64: per q row {hi, mid, lo, 0 x 5} 16-bit parts of -lse
+  const uint8_t* aux_delta;  // ... and of -delta (16 bytes per row each)
   void* dq;
   void* dk;
   void* dv;

@@ -22,6 +22,8 @@ inline void fill_bwd_args(BwdArgs& a, const SplashParams& p, bool dense, bool se
   a.seg_kv_ranges = nullptr;
   a.lse = p.lse;
   a.delta = p.delta;
+  a.aux_lse = nullptr;
+  a.aux_delta = nullptr;
   a.dq = p.dq;
   a.dk = p.dk;
   a.dv = p.dv;

@@ -126,6 +126,53 @@ __global__ void __launch_bounds__(256) dq_transpose_cast_kernel(const float* __r
   }
 }
 
+// Splits -x into three 16-bit floats whose sum is -x to f32 precision, as the eight 16-bit
+// values {hi, mid, lo, 0, 0, 0, 0, 0} per row that the 128-row fused backward (head_dim 64)
+// multiplies by {1, 1, 1, 0, ...} in one extra K = 16 slice of its score products.  Rows whose
+// lse is mask_value (they saw no key) get a large negative value instead, which makes their P zero.
+template <bool BF16>
+__device__ __forceinline__ uint4 split3_neg(float x, bool sentinel) {
+  float v = sentinel ? (BF16 ? -1.0e30f : -60000.f) : -x;
+  uint32_t h[3];
+#pragma unroll
+  for (int i = 0; i < 3; ++i) {
+    if constexpr (BF16) {
+      const __nv_bfloat16 b = __float2bfloat16_rn(v);
+      h[i] = *reinterpret_cast<const uint16_t*>(&b);
+      v -= __bfloat162float(b);
+    } else {
+      const __half b = __float2half_rn(v);
+      h[i] = *reinterpret_cast<const uint16_t*>(&b);
+      v -= __half2float(b);
+    }
+  }
+  return make_uint4(h[0] | (h[1] << 16), h[2], 0u, 0u);
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(256) fold_operands_kernel(const float* __restrict__ lse, const float* __restrict__ delta,
+                                                            uint4* __restrict__ aux_lse, uint4* __restrict__ aux_delta,
+                                                            long long rows, float mask_value) {
+  const long long r = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+  if (r >= rows) return;
+  const float l = lse[r];
+  aux_lse[r] = split3_neg<BF16>(l, l == mask_value);
+  aux_delta[r] = split3_neg<BF16>(delta[r], false);
+}
+
+int launch_fold_operands(const float* lse, const float* delta, void* aux_lse, void* aux_delta, long long rows,
+                         float mask_value, int dtype, cudaStream_t stream) {
+  const unsigned grid = static_cast<unsigned>((rows + 255) / 256);
+  if (dtype == SPLASH_DTYPE_BF16)
+    fold_operands_kernel<true><<<grid, 256, 0, stream>>>(lse, delta, static_cast<uint4*>(aux_lse),
+                                                         static_cast<uint4*>(aux_delta), rows, mask_value);
+  else
+    fold_operands_kernel<false><<<grid, 256, 0, stream>>>(lse, delta, static_cast<uint4*>(aux_lse),
+                                                          static_cast<uint4*>(aux_delta), rows, mask_value);
+  SPLASH_CUDA_CHECK(cudaGetLastError());
+  return SPLASH_OK;
+}
+
 // (min, max) of every 64 consecutive segment ids: one warp per chunk, two ids per lane.
 // `out` holds the q part [batch, q_len / 64] followed by the kv part [batch, kv_len / 64].
 __global__ void __launch_bounds__(256) seg_ranges_kernel(const int32_t* __restrict__ seg_q,

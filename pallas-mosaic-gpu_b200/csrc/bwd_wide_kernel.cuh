@@ -58,27 +58,44 @@ enum WideSite : int {
   kWSiteWrReady,
 };
 
+template <int D_>
 struct WideLayout {
-  static constexpr int D = 128;
+  static_assert(D_ == 64 || D_ == 128, "head_dim 64 or 128");
+  static constexpr int D = D_;
   static constexpr int kRows = 128;  // kv rows per CTA
   static constexpr int BC = 128;     // q rows per step
-  static constexpr int kTile = kRows * D * 2;  // every 16-bit tile here is 32 KB
-  static constexpr int kBox = kRows * 128;     // one 64-element-wide box of a tile
+  static constexpr int kBox = kRows * 128;        // one 64-element-wide box of a 128-row tile: 16 KB
+  static constexpr int kTile = kRows * D * 2;     // a K, V, Q or dO tile
+  // At head_dim 64 the dQ^T product keeps M = 128: its A operand's second 64 rows are a second
+  // copy of the K tile, so the upper half of the result repeats the lower half and is not stored.
+  static constexpr int kKDupBytes = D == 64 ? kBox : 0;
+  static constexpr int kDsBytes = kRows * BC * 2;  // dS^T as an MMA operand
   static constexpr int kSlots = 2;
   static constexpr int kVecBytes = BC * 4;
   // Shared memory map (bytes from the 1024-aligned base).
-  static constexpr int kOffK = 0, kOffV = kTile, kOffQ = 2 * kTile, kOffDo = 4 * kTile, kOffDs = 5 * kTile;
-  static constexpr int kOffDqStage = 6 * kTile;  // per writer warp: kDqBufs f32 tiles of [32 d, 32 q]
+  static constexpr int kOffK = 0, kOffV = kTile + kKDupBytes, kOffQ = kOffV + kTile, kOffDo = kOffQ + kSlots * kTile;
+  static constexpr int kOffDs = kOffDo + kTile;
+  static constexpr int kOffDqStage = kOffDs + kDsBytes;  // per writer warp: kDqBufs f32 tiles of [32 d, 32 q]
   static constexpr int kDqBufs = 2;
   static constexpr int kDqBoxBytes = 32 * 32 * 4;
-  static constexpr int kOffLse = 7 * kTile, kOffDelta = kOffLse + kSlots * kVecBytes;
-  static constexpr int kOffBars = kOffDelta + kSlots * kVecBytes;
+  static constexpr int kOffLse = kOffDqStage + 4 * kDqBufs * kDqBoxBytes, kOffDelta = kOffLse + kSlots * kVecBytes;
+  // Folded operands (head_dim 64, where shared memory has the room): -lse and -delta are subtracted
+  // inside the S^T and dP^T products by one extra K = 16 slice each.  Per q row eight 16-bit values
+  // {hi, mid, lo, 0, ...} whose sum is -lse (or -delta) to f32 precision -- the first 8 x 8 core
+  // matrices of an unswizzled K-major tile -- against {1, 1, 1, 0, ...} per kv row; the second half of
+  // K is a shared block of zeros.
+  static constexpr bool kFold = D == 64;
+  static constexpr int kAuxTile = BC * 16;
+  static constexpr int kOffAux = kOffDelta + kSlots * kVecBytes;                  // per Q slot: [-lse tile | -delta tile]
+  static constexpr int kOffOnes = kOffAux + (kFold ? kSlots * 2 * kAuxTile : 0);
+  static constexpr int kOffZeros = kOffOnes + (kFold ? kAuxTile : 0);
+  static constexpr int kOffBars = kOffZeros + (kFold ? kAuxTile : 0);
   static constexpr int kBarBytes = 256;
   static constexpr int kListSteps = 256;  // capacity of the list of block steps that survive segment skipping
   static constexpr int kOffList = kOffBars + kBarBytes;
   static constexpr int kSmemBytes = kOffList + kListSteps * 2;
   // Tensor memory columns.
-  static constexpr int kColS = 0, kColDp = 128, kColDk = 256, kColDv = 384;
+  static constexpr int kColS = 0, kColDp = 128, kColDk = 256, kColDv = 256 + D;
   static constexpr int kTmemCols = 512;
   static constexpr int kEwThreads = 256;
   static constexpr int kThreads = 512;  // 2 elementwise warpgroups, writer warpgroup, producer warpgroup
@@ -97,20 +114,20 @@ struct WideBarriers {
   uint32_t dead;
   uint32_t n_eff;  // block steps left after segment skipping
 };
-static_assert(sizeof(WideBarriers) <= WideLayout::kBarBytes, "barrier block");
+static_assert(sizeof(WideBarriers) <= WideLayout<128>::kBarBytes, "barrier block");
 
 #define SPLASH_WBAR(field, idx) \
   (bars_u32 + static_cast<uint32_t>(offsetof(WideBarriers, field)) + 8u * static_cast<uint32_t>(idx))
 
 // PLAIN: no soft-cap and no segment ids -- that code is compiled out.  Streamed (dense
 // int8) mask blocks are not handled here; calls that carry them take the 64-row kernel.
-template <bool PLAIN, bool BF16>
-__global__ void __launch_bounds__(WideLayout::kThreads, 1)
+template <int HEAD_DIM, bool PLAIN, bool BF16>
+__global__ void __launch_bounds__(WideLayout<HEAD_DIM>::kThreads, 1)
 splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                        const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
                        const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv,
                        const __grid_constant__ CUtensorMap tm_dqacc, const BwdArgs a) {
-  using L = WideLayout;
+  using L = WideLayout<HEAD_DIM>;
   constexpr int D = L::D;
   constexpr int kRows = L::kRows;
   constexpr int kEwWarps = 8;
@@ -129,6 +146,11 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   const uint32_t dqs_u32 = base_u32 + L::kOffDqStage;
   const uint32_t lse_u32 = base_u32 + L::kOffLse;
   const uint32_t delta_u32 = base_u32 + L::kOffDelta;
+  const uint32_t aux_u32 = base_u32 + L::kOffAux;
+  const uint32_t ones_u32 = base_u32 + L::kOffOnes;
+  const uint32_t zeros_u32 = base_u32 + L::kOffZeros;
+  // With soft-capping lse has to be subtracted after the cap, so only delta is folded then.
+  const bool fold_lse = L::kFold && !(soft_cap > 0.f);
   const uint32_t bars_u32 = base_u32 + L::kOffBars;
   const uint32_t abort_u32 = bars_u32 + static_cast<uint32_t>(offsetof(WideBarriers, abort_flag));
   const uint32_t dead_u32 = bars_u32 + static_cast<uint32_t>(offsetof(WideBarriers, dead));
@@ -198,6 +220,16 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     });
     if (lane == 0) sts32(neff_u32, static_cast<uint32_t>(kept));
   }
+  if constexpr (L::kFold) {
+    if (threadIdx.x >= 64 && threadIdx.x < 64 + 256) {
+      // 128 rows of {1, 1, 1, 0, 0, 0, 0, 0}, and 2 KB of zeros.
+      const uint32_t i = threadIdx.x - 64;
+      const uint32_t one = BF16 ? 0x3f80u : 0x3c00u;
+      if (i < 128) sts128(ones_u32 + i * 16, make_uint4(one | (one << 16), one, 0u, 0u));
+      else sts128(zeros_u32 + (i - 128) * 16, make_uint4(0u, 0u, 0u, 0u));
+      fence_proxy_async_smem();
+    }
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -222,9 +254,10 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         prefetch_tensormap(&tm_q);
         prefetch_tensormap(&tm_k);
         prefetch_tensormap(&tm_v);
-        mbar_arrive_expect_tx(SPLASH_WBAR(kv_full, 0), 2 * L::kTile);
+        mbar_arrive_expect_tx(SPLASH_WBAR(kv_full, 0), 2 * L::kTile + L::kKDupBytes);
 #pragma unroll
         for (int c = 0; c < D / 64; ++c) tma_load_2d(k_u32 + c * L::kBox, &tm_k, c * 64, kv_row0, SPLASH_WBAR(kv_full, 0));
+        if constexpr (L::kKDupBytes > 0) tma_load_2d(k_u32 + L::kTile, &tm_k, 0, kv_row0, SPLASH_WBAR(kv_full, 0));
 #pragma unroll
         for (int c = 0; c < D / 64; ++c) tma_load_2d(v_u32 + c * L::kBox, &tm_v, c * 64, kv_row0, SPLASH_WBAR(kv_full, 0));
       }
@@ -235,11 +268,17 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         if (t >= 2 && !warp_wait(SPLASH_WBAR(q_empty, slot), ((t >> 1) & 1) ^ 1, ctx, kWSiteQEmpty, t)) break;
         if (elect_one()) {
           const uint32_t bar = SPLASH_WBAR(q_full, slot);
-          mbar_arrive_expect_tx(bar, L::kTile + 2 * L::kVecBytes);
+          mbar_arrive_expect_tx(bar, L::kTile + (L::kFold ? 2 * L::kAuxTile + L::kVecBytes : 2 * L::kVecBytes));
 #pragma unroll
           for (int c = 0; c < D / 64; ++c) tma_load_2d(q_u32 + slot * L::kTile + c * L::kBox, &tm_q, c * 64, q_row, bar);
           bulk_load_1d(lse_u32 + slot * L::kVecBytes, a.lse + q_row, L::kVecBytes, bar);
-          bulk_load_1d(delta_u32 + slot * L::kVecBytes, a.delta + q_row, L::kVecBytes, bar);
+          if constexpr (L::kFold) {
+            const size_t aux_off = static_cast<size_t>(q_row) * 16;
+            bulk_load_1d(aux_u32 + slot * 2 * L::kAuxTile, a.aux_lse + aux_off, L::kAuxTile, bar);
+            bulk_load_1d(aux_u32 + slot * 2 * L::kAuxTile + L::kAuxTile, a.aux_delta + aux_off, L::kAuxTile, bar);
+          } else {
+            bulk_load_1d(delta_u32 + slot * L::kVecBytes, a.delta + q_row, L::kVecBytes, bar);
+          }
         }
       }
     } else if (warp == kProducerWarp0 + 2 && total > 0) {
@@ -271,6 +310,12 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           umma_ss2_w(tmem + d_col, a_lo + o, kDescHi, b_lo + o, kDescHi, kIdescScore, kk > 0);
         }
       };
+      // One more K = 16 slice: D[kv, q] += sum_k ones[kv, k] * aux[q, k] = -lse[q] (or -delta[q]);
+      // both operands unswizzled K-major, the second half of K read from the block of zeros.
+      auto issue_fold = [&](uint32_t d_col, uint32_t b_tile) {
+        umma_ss2_w(tmem + d_col, desc_lo_plain(ones_u32, zeros_u32 - ones_u32), desc_hi_plain(128),
+                   desc_lo_plain(b_tile, zeros_u32 - b_tile), desc_hi_plain(128), kIdescScore, 1u);
+      };
       // A = packed 16-bit values the elementwise warps left in tensor memory: q columns
       // 0-63 packed into columns 0-31 of the region, q columns 64-127 into columns 64-95
       // (each warpgroup packs into its own half).  B = a [128 q, 128 d] tile read MN-major.
@@ -294,12 +339,14 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       if (ok) {
         tc_fence_after();
         issue_scores(L::kColS, k_u32, q_u32);
+        if (fold_lse) issue_fold(L::kColS, aux_u32);
         umma_commit_w(SPLASH_WBAR(s_ready, 0));
         ok = warp_wait(SPLASH_WBAR(do_full, 0), 0, ctx, kWSiteMmaDo, 0);
       }
       if (ok) {
         tc_fence_after();
         issue_scores(L::kColDp, v_u32, do_u32);
+        if constexpr (L::kFold) issue_fold(L::kColDp, aux_u32 + L::kAuxTile);
         umma_commit_w(SPLASH_WBAR(dp_ready, 0));
         for (int t = 0; t < total; ++t) {
           const int slot = t & 1, nslot = slot ^ 1;
@@ -315,6 +362,7 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             SPLASH_TRACE_MARK(0, t, 2);
             tc_fence_after();
             issue_scores(L::kColS, k_u32, q_u32 + nslot * L::kTile);         // S^T(t+1) over P^T(t)
+            if (fold_lse) issue_fold(L::kColS, aux_u32 + nslot * 2 * L::kAuxTile);
             umma_commit_w(SPLASH_WBAR(s_ready, 0));
           }
           SPLASH_TRACE_MARK(0, t, 3);
@@ -334,6 +382,7 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           if (t + 1 < total) {
             tc_fence_after();
             issue_scores(L::kColDp, v_u32, do_u32);                            // dP^T(t+1)
+            if constexpr (L::kFold) issue_fold(L::kColDp, aux_u32 + nslot * 2 * L::kAuxTile + L::kAuxTile);
             umma_commit_w(SPLASH_WBAR(dp_ready, 0));
           }
         }
@@ -356,11 +405,15 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       SPLASH_TRACE_MARK(2, t, 1);
       tc_fence_after();
       uint32_t acc[128];
+      const bool mine = wq * 32 < D;  // at head_dim 64 the upper two quarters repeat the lower ones
+      if (mine) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld32(dq_tmem + c * 32, acc + c * 32);
-      tmem_wait_ld();
+        for (int c = 0; c < 4; ++c) tmem_ld32(dq_tmem + c * 32, acc + c * 32);
+        tmem_wait_ld();
+      }
       tc_fence_before();
       mbar_arrive(SPLASH_WBAR(dq_free, 0));
+      if (!mine) continue;
       SPLASH_TRACE_MARK(2, t, 2);
       const int x = qblk * 128;
       const int y = (b * a.heads + it.head()) * D + wq * 32;
@@ -475,28 +528,37 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           // Masked entries and rows that saw no key (lse == mask_value) get an exponent of
           // -inf, i.e. P = 0.  FULL blocks without segment ids need neither test: a row whose
           // lse is mask_value never meets a FULL block.
+          // Where the products fold lse in (head_dim 64, no soft-cap) the scores arrive with lse
+          // already subtracted and rows that saw no key carry a large negative value: P = exp2(S^T log2e).
           auto body = [&](auto cap_c, auto mask_c) {
             constexpr bool kCap = decltype(cap_c)::value, kMask = decltype(mask_c)::value;
+            constexpr bool kNeedLse = kCap || !L::kFold;
 #pragma unroll
             for (int g = 0; g < 16; ++g) {
-              const uint4 lw = lds128(vec + g * 16);
-              const uint32_t lraw[4] = {lw.x, lw.y, lw.z, lw.w};
+              float nl[4] = {0.f, 0.f, 0.f, 0.f};
+              if constexpr (kNeedLse) {
+                const uint4 lw = lds128(vec + g * 16);
+                const uint32_t lraw[4] = {lw.x, lw.y, lw.z, lw.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float lse_e = __uint_as_float(lraw[e]);
+                  nl[e] = lse_e * -kLog2e;
+                  if constexpr (kMask) {
+                    if (lse_e == a.mask_value) nl[e] = -INFINITY;
+                  }
+                }
+              }
               float pv[4];
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
                 const int i = g * 4 + e;
-                const float lse_e = __uint_as_float(lraw[e]);
-                float nl = lse_e * -kLog2e;
-                if constexpr (kMask) {
-                  if (lse_e == a.mask_value) nl = -INFINITY;
-                }
                 float sval = pf[i], keep = 1.f;
                 if constexpr (kCap) {
                   const float th = tanh_approx(sval * inv_cap);
                   sval = cap * th;
                   keep = fmaf(-th, th, 1.f);
                 }
-                float x = fmaf(sval, kLog2e, nl);
+                float x = kNeedLse ? fmaf(sval, kLog2e, nl[e]) : sval * kLog2e;
                 if constexpr (kMask) {
                   if (!((vis[i >> 5] >> (i & 31)) & 1u)) x = -INFINITY;
                 }
@@ -533,15 +595,27 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           tmem_ld32(tmem_row + L::kColDp + col0 + c * 32, dpraw);
           tmem_wait_ld();
           uint32_t dspk[16];
-          const uint32_t vec = delta_u32 + slot * L::kVecBytes + (col0 + c * 32) * 4;
+          if constexpr (L::kFold) {
+            // dP^T arrives with delta already subtracted.
 #pragma unroll
-          for (int g = 0; g < 8; ++g) {
-            const uint4 dw = lds128(vec + g * 16);
-            const int i = c * 32 + g * 4;
-            dspk[g * 2] = pack2<BF16>(pf[i + 0] * (__uint_as_float(dpraw[g * 4 + 0]) - __uint_as_float(dw.x)),
-                                      pf[i + 1] * (__uint_as_float(dpraw[g * 4 + 1]) - __uint_as_float(dw.y)));
-            dspk[g * 2 + 1] = pack2<BF16>(pf[i + 2] * (__uint_as_float(dpraw[g * 4 + 2]) - __uint_as_float(dw.z)),
-                                          pf[i + 3] * (__uint_as_float(dpraw[g * 4 + 3]) - __uint_as_float(dw.w)));
+            for (int g = 0; g < 8; ++g) {
+              const int i = c * 32 + g * 4;
+              dspk[g * 2] = pack2<BF16>(pf[i + 0] * __uint_as_float(dpraw[g * 4 + 0]),
+                                        pf[i + 1] * __uint_as_float(dpraw[g * 4 + 1]));
+              dspk[g * 2 + 1] = pack2<BF16>(pf[i + 2] * __uint_as_float(dpraw[g * 4 + 2]),
+                                            pf[i + 3] * __uint_as_float(dpraw[g * 4 + 3]));
+            }
+          } else {
+            const uint32_t vec = delta_u32 + slot * L::kVecBytes + (col0 + c * 32) * 4;
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              const uint4 dw = lds128(vec + g * 16);
+              const int i = c * 32 + g * 4;
+              dspk[g * 2] = pack2<BF16>(pf[i + 0] * (__uint_as_float(dpraw[g * 4 + 0]) - __uint_as_float(dw.x)),
+                                        pf[i + 1] * (__uint_as_float(dpraw[g * 4 + 1]) - __uint_as_float(dw.y)));
+              dspk[g * 2 + 1] = pack2<BF16>(pf[i + 2] * (__uint_as_float(dpraw[g * 4 + 2]) - __uint_as_float(dw.z)),
+                                            pf[i + 3] * (__uint_as_float(dpraw[g * 4 + 3]) - __uint_as_float(dw.w)));
+            }
           }
           tmem_st16(tmem_row + L::kColDp + col0 + c * 16, dspk);
           // dS^T staged as [kv row][q], two boxes of 64 q columns, 128-byte swizzle.

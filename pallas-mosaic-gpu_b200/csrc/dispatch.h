@@ -34,6 +34,15 @@ int launch_delta(const void* o, const void* d_out, float* delta, long long rows,
                  cudaStream_t stream, float* zero = nullptr, int zero_floats_per_row = 0);
 int launch_dq_transpose_cast(const float* acc, void* dq, long long batch_heads, int head_dim, int q_len, int dtype,
                              cudaStream_t stream);
+// -lse and -delta of every q row as three 16-bit parts each (16 bytes per row and array): the
+// operands of the slice that the 128-row fused backward adds to its score products at head_dim 64.
+int launch_fold_operands(const float* lse, const float* delta, void* aux_lse, void* aux_delta, long long rows,
+                         float mask_value, int dtype, cudaStream_t stream);
+// Bytes of those two arrays together (they follow the f32 dQ accumulator in the fused backward's scratch).
+inline long long fold_operand_bytes(const SplashParams& p) {
+  return p.head_dim == 64 ? 2ll * 16 * p.batch * p.heads * p.q_len : 0;
+}
+
 // Fills p.seg_ranges (when given, with segment ids) with the (min, max) id of every 64 positions.
 int launch_seg_ranges(const SplashParams& p, cudaStream_t stream);
 
