@@ -478,7 +478,7 @@ def run_ours(args):
   sa.check_device_status()
 
   # ---- one CUDA graph of the step (the library's calls are capturable: no allocation, no sync) ------
-  graph, graph_error = None, None
+  graph, fwd_graph, graph_error = None, None, None
   if not args.no_graph and n_local > 0:
     try:
       side = torch.cuda.Stream(dev)
@@ -494,6 +494,15 @@ def run_ours(args):
       graph.replay()
       torch.cuda.synchronize(dev)
       sa.check_device_status()
+      if not wl.forward_only:
+        # The forward on its own (with its logsumexp residual), for the forward / backward split.
+        qd, kd, vd = q.detach(), k.detach(), v.detach()
+        kernel(qd, kd, vd, seg, save_residuals=True)
+        fwd_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(fwd_graph):
+          fwd_graph_out = kernel(qd, kd, vd, seg, save_residuals=True)
+        fwd_graph.replay()
+        torch.cuda.synchronize(dev)
     except Exception as e:  # capture is an optimisation of the launch path only
       graph = None
       graph_error = f"{type(e).__name__}: {str(e).splitlines()[0][:160]}"
@@ -529,32 +538,39 @@ def run_ours(args):
     ms = start.elapsed_time(end)
     fwd = bwd = float("nan")
     if split and not wl.forward_only and n_local:
-      fwd = float(np.mean([e[0].elapsed_time(e[1]) for e in ev]))
-      bwd = float(np.mean([e[1].elapsed_time(e[2]) for e in ev]))
+      # Medians: an eager step that the host was late to launch would otherwise count idle time.
+      fwd = float(np.median([e[0].elapsed_time(e[1]) for e in ev]))
+      bwd = float(np.median([e[1].elapsed_time(e[2]) for e in ev]))
     return ms, fwd, bwd, (first, sampler.mark())
 
   for _ in range(3):   # eager warm-up again: the capture above changed the allocator's state
     step()
-  eager_ms, fwd_in_step_ms, bwd_ms, eager_marks = timed_loop(args.steps, False, split=True)
+  eager_ms, fwd_in_step_ms, eager_bwd_ms, eager_marks = timed_loop(args.steps, False, split=True)
+  bwd_ms = eager_bwd_ms
   # The forward on its own, as the reference's benchmark times it (tools/bench.py:70-76: the forward
-  # with its logsumexp residual in a loop of its own, then forward + backward).
+  # with its logsumexp residual in a loop of its own, then forward + backward): a replay of its graph
+  # when there is one, eager calls otherwise.
   fwd_ms = eager_ms / args.steps
-  if not wl.forward_only and n_local:
+  if not wl.forward_only:
     qd, kd, vd = q.detach(), k.detach(), v.detach()
     for _ in range(3):
-      kernel(qd, kd, vd, seg, save_residuals=True)
+      if n_local:
+        kernel(qd, kd, vd, seg, save_residuals=True)
     barrier()
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     f0.record()
     for _ in range(args.steps):
-      kernel(qd, kd, vd, seg, save_residuals=True)
+      if fwd_graph is not None:
+        fwd_graph.replay()
+      elif n_local:
+        kernel(qd, kd, vd, seg, save_residuals=True)
     f1.record()
     barrier()
     fwd_ms = f0.elapsed_time(f1) / args.steps
-  elif not wl.forward_only:
-    barrier()
-    barrier()
   graph_ms, _, _, graph_marks = timed_loop(args.steps, True) if graph is not None else (float("nan"), 0, 0, eager_marks)
+  if graph is not None and fwd_graph is not None and graph_ms <= eager_ms:
+    # Backward = replayed step minus replayed forward: free of host launch gaps.
+    bwd_ms = graph_ms / args.steps - fwd_ms
   sa.check_device_status()
 
   # A loop of at least two seconds: the clocks settle at the power cap there.
@@ -648,14 +664,15 @@ def run_ours(args):
       check = dict(gathered_units=int(units.shape[0]), recomputed_on_rank0=n_checked, bit_identical=same,
                    how="NCCL all_gather of the forward outputs, then one unit per rank recomputed on rank 0")
 
-  stats = [eager_ms, graph_ms if graph is not None else -1.0, e2e_ms, fwd_ms, bwd_ms, sus_ms,
-           fwd_in_step_ms if fwd_in_step_ms == fwd_in_step_ms else -1.0]
+  nan_to = lambda x: x if x == x else -1.0
+  stats = [eager_ms, graph_ms if graph is not None else -1.0, e2e_ms, fwd_ms, nan_to(bwd_ms), sus_ms,
+           nan_to(fwd_in_step_ms), nan_to(eager_bwd_ms)]
   times = torch.tensor(stats, dtype=torch.float64, device=dev)
   sums = torch.tensor([float(h2d_local), float(d2h_local), local_fwd_flops], dtype=torch.float64, device=dev)
   if dist is not None:
     dist.all_reduce(times, op=dist.ReduceOp.MAX)
     dist.all_reduce(sums, op=dist.ReduceOp.SUM)
-  eager_ms, graph_ms, e2e_ms, fwd_ms, bwd_ms, sus_ms, fwd_in_step_ms = times.tolist()
+  eager_ms, graph_ms, e2e_ms, fwd_ms, bwd_ms, sus_ms, fwd_in_step_ms, eager_bwd_ms = times.tolist()
   h2d, d2h, fwd_flops_sum = sums.tolist()
   assert abs(fwd_flops_sum - fwd_flops) <= 1e-6 * fwd_flops, "the ranks' units do not add up to the workload"
 
@@ -756,7 +773,9 @@ def run_ours(args):
                      eager_ms_per_step=eager_ms / args.steps,
                      graph_ms_per_step=graph_ms / args.steps if graph_ms > 0 else None, graph_error=graph_error),
         fwd_tflops=fwd_tflops, fwd_ms=fwd_ms, bwd_ms=None if wl.forward_only else bwd_ms,
-        fwd_ms_inside_step=None if wl.forward_only else fwd_in_step_ms, fwd256_tflops=fwd256,
+        eager_split=None if wl.forward_only else dict(fwd_ms=fwd_in_step_ms, bwd_ms=eager_bwd_ms,
+                                                      note="medians of events between the halves of eager steps"),
+        fwd256_tflops=fwd256,
         roofline=roofline, roofline_fwd=roofline_fwd, sustained=sus, cpu_baseline=cpu, sdpa=sdpa, check=check,
         e2e=dict(value=fb_flops / (e2e_ms / args.steps * 1e-3) / 1e12, unit=UNIT,
                  h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h, ms_per_step=e2e_ms / args.steps),
