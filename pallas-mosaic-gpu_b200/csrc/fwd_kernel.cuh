@@ -581,6 +581,7 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
 
         // ---- online softmax with a stale maximum --------------------------------
+        if ((warp & 3) == 0) SPLASH_TRACE_MARK(1 + grp, s, 6);
         float mx0 = max3(sv[0], sv[1], sv[2]), mx1 = max3(sv[3], sv[4], sv[5]);
         float mx2 = fmaxf(sv[6], sv[7]), mx3 = sv[8];
 #pragma unroll
