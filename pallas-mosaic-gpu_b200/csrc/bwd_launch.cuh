@@ -118,7 +118,11 @@ int launch_bwd_row_typed(const SplashParams& p, cudaStream_t stream) {
   using L = RowLayout<D, DV, BC>;
   const bool dense = p.partial_blocks != nullptr;
   const bool seg = p.seg_q != nullptr;
-  const size_t smem = L::smem_bytes(p.num_stages, dense, seg);
+  // The list of block steps that survive segment skipping needs max_steps 16-bit entries;
+  // without room for it the kernel runs every scheduled step.
+  const bool skipping = seg && p.seg_ranges != nullptr && p.max_steps < (1 << 15) &&
+                        L::smem_bytes(p.num_stages, dense, seg, p.max_steps) <= kMaxDynamicSmem;
+  const size_t smem = L::smem_bytes(p.num_stages, dense, seg, skipping ? p.max_steps : 0);
   if (smem > kMaxDynamicSmem) {
     char d[96];
     snprintf(d, sizeof d, "%zu > %zu bytes; reduce num_stages or the sub-block sizes", smem, kMaxDynamicSmem);
@@ -138,6 +142,8 @@ int launch_bwd_row_typed(const SplashParams& p, cudaStream_t stream) {
   if ((rc = make_tmap_2d(&tm_dq, p.dq, dt, 2, q_rows, D, 128, 64, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   BwdArgs a;
   fill_bwd_args(a, p, dense, seg);
+  a.seg_q_ranges = skipping ? seg_q_ranges(p) : nullptr;
+  a.seg_kv_ranges = skipping ? seg_kv_ranges(p) : nullptr;
   auto kernel = splash_bwd_row_kernel<D, DV, BC, BF16>;
   if ((rc = opt_in_smem(kernel, smem))) return rc;
   const unsigned grid = static_cast<unsigned>(a.q_blocks) * p.heads * p.batch;

@@ -44,8 +44,10 @@ struct RowLayout {
   static constexpr int kThreads = 384;
   static_assert(kTmemUsed <= 512, "tensor memory budget");
 
-  __host__ __device__ static size_t smem_bytes(int stages, bool dense, bool seg) {
+  // `list_steps`: capacity of the list of block steps that survive segment skipping (0 = no list).
+  __host__ __device__ static size_t smem_bytes(int stages, bool dense, bool seg, int list_steps = 0) {
     size_t b = 1024;
+    b += (static_cast<size_t>(list_steps) * 2 + 15) & ~static_cast<size_t>(15);
     b += kQBytes + kDoBytes;
     b += static_cast<size_t>(stages) * (kKStage + kVStage);
     if (seg) b += static_cast<size_t>(stages) * kVecStage;
@@ -63,6 +65,7 @@ struct RowBarriers {
   uint32_t tmem_base;
   uint32_t abort_flag;
   uint32_t dead;
+  uint32_t n_eff;  // block steps left after segment skipping
 };
 
 #define SPLASH_RBAR(field, idx) \
@@ -91,6 +94,10 @@ splash_bwd_row_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const uint32_t abort_u32 = bars_u32 + static_cast<uint32_t>(offsetof(RowBarriers, abort_flag));
   const uint32_t dead_u32 = bars_u32 + static_cast<uint32_t>(offsetof(RowBarriers, dead));
   const uint32_t tmem_slot_u32 = bars_u32 + static_cast<uint32_t>(offsetof(RowBarriers, tmem_base));
+  const uint32_t neff_u32 = bars_u32 + static_cast<uint32_t>(offsetof(RowBarriers, n_eff));
+  const uint32_t list_u32 = bars_u32 + 128u;  // surviving block steps, 16 bits each
+  static_assert(sizeof(RowBarriers) <= 128, "step list overlaps the barriers");
+  const bool has_list = a.has_seg && a.seg_q_ranges != nullptr;
 
   const int warp = uniform_warp_index();
   const int lane = threadIdx.x & 31;
@@ -101,8 +108,7 @@ splash_bwd_row_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const int b = hb / a.heads;
   const int mh = a.mask_heads > 1 ? h : 0;
   const int qi = a.block_order[mh * a.q_blocks + order_idx];
-  const int n = a.num_steps[mh * a.q_blocks + qi];
-  const int total = n * kSub;
+  const int n_sched = a.num_steps[mh * a.q_blocks + qi];
   const int sched_off = (mh * a.q_blocks + qi) * a.max_steps;
   const int q_row0 = (b * a.heads + h) * a.q_len + qi * kRows;
 
@@ -126,12 +132,27 @@ splash_bwd_row_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   if (warp == kEwWarps + 1) {
     tmem_alloc(tmem_slot_u32, L::kTmemCols);
     tmem_relinquish();
+  } else if (warp == 1 && has_list) {
+    // Block steps whose q and kv segment-id ranges can meet; every role leaves out the others.
+    const int2* qt = a.seg_q_ranges + static_cast<size_t>(b) * (a.q_len / kSegChunk);
+    const int2* kt = a.seg_kv_ranges + static_cast<size_t>(b) * (a.kv_len / kSegChunk);
+    const SegRange qr = seg_range(qt, qi * (kRows / kSegChunk), kRows / kSegChunk);
+    const int kept = build_step_list(list_u32, n_sched, lane, [&](int s) {
+      const int j = a.block_list[sched_off + s];
+      return seg_classify(qr, seg_range(kt, j * (128 / kSegChunk), 128 / kSegChunk));
+    });
+    if (lane == 0) sts32(neff_u32, static_cast<uint32_t>(kept));
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = lds32(tmem_slot_u32);
   const WaitCtx ctx{abort_u32};
+  const int n = has_list ? static_cast<int>(lds32(neff_u32)) : n_sched;
+  const int total = n * kSub;
+  // Entry e of the CTA's block-step sequence: index into the schedule lists, top bit set
+  // when the block needs no segment comparison.
+  auto step_at = [&](int e) -> uint32_t { return has_list ? lds16(list_u32 + 2u * e) : static_cast<uint32_t>(e); };
   constexpr uint32_t kDescHi = desc_hi(1024);
 
   if (warp >= kEwWarps) {
@@ -153,7 +174,7 @@ splash_bwd_row_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       int slot = 0;
       uint32_t phase = 0;
       for (int t = 0; t < total; ++t) {
-        const int s = t / kSub, sb = t % kSub;
+        const int s = static_cast<int>(step_at(t / kSub) & 0x7fffu), sb = t % kSub;
         const int j = a.block_list[sched_off + s];
         const int kv_row = kv_row0 + j * 128 + sb * BC;
         if (t >= stages && !warp_wait(SPLASH_RBAR(empty, slot), phase ^ 1, ctx, kRSiteTmaEmpty, t)) break;
@@ -275,7 +296,9 @@ splash_bwd_row_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       uint32_t phase = 0;
 
       for (int t = 0; t < total; ++t) {
-        const int s = t / kSub, sb = t % kSub;
+        const uint32_t entry = step_at(t / kSub);
+        const int s = static_cast<int>(entry & 0x7fffu), sb = t % kSub;
+        const bool seg_compare = a.has_seg && !(entry & kSegUniformBit);
         const int j = a.block_list[sched_off + s];
         const bool partial = a.block_kind[sched_off + s] == SPLASH_BLOCK_PARTIAL;
         if (!warp_wait(SPLASH_RBAR(full, slot), phase, ctx, kRSiteEwFull, t)) { alive = false; break; }
@@ -301,7 +324,7 @@ splash_bwd_row_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             // One bit per element: 16 bytes per q row, bit = kv column inside the block.
             vis &= lds32(mask_u32 + slot * L::kMaskStage + row * 16 + (sb * BC + col0 + c * 32) / 8);
           }
-          if (a.has_seg) {
+          if (seg_compare) {
 #pragma unroll
             for (int g = 0; g < 8; ++g) {
               const uint4 sg = lds128(seg_u32 + slot * L::kVecStage + (col0 + c * 32 + g * 4) * 4);
