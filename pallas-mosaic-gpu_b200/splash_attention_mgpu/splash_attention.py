@@ -45,7 +45,9 @@ _TORCH_DTYPES = {torch.bfloat16: _ffi.DTYPE_BF16, torch.float16: _ffi.DTYPE_F16}
 # ---------------------------------------------------------------------------
 
 _status_words: dict = {}
-_status_mirrors: dict = {}   # device key -> (pinned host copy of the word, event recorded after the copy)
+# device key -> (pinned host copy of the word, event recorded after the copy, side stream that carries
+# the copy, event that marks the kernels the copy has to follow)
+_status_mirrors: dict = {}
 
 
 def _status_word(device: torch.device) -> torch.Tensor:
@@ -88,7 +90,7 @@ def _poll_status(device) -> None:
   mirror = _status_mirrors.get((device.type, device.index))
   if mirror is None or torch.cuda.is_current_stream_capturing():
     return
-  host, event = mirror
+  host, event = mirror[:2]
   if event.query() and int(host[0]) != 0:
     _status_mirrors.pop((device.type, device.index), None)
     _raise_device_status(_status_word(device), host.tolist())
@@ -97,7 +99,10 @@ def _poll_status(device) -> None:
 def _maybe_check(device) -> None:
   """End of a call.  SPLASH_CHECK_STATUS: "1" synchronises and checks now, "0" checks nothing, anything
   else (the default) queues a 16-byte copy of the status word to pinned host memory behind the
-  kernels; the next call on this device, or `check_device_status`, looks at it."""
+  kernels; the next call on this device, or `check_device_status`, looks at it.  The copy runs on a
+  stream of its own that waits for the kernels: on the caller's stream it would sit in the copy
+  engine's queue behind whatever bulk device-to-host copies the caller has in flight and hold up the
+  caller's next kernels until those are done."""
   mode = os.environ.get("SPLASH_CHECK_STATUS", "async")
   if mode == "1":
     check_device_status(device)
@@ -107,11 +112,15 @@ def _maybe_check(device) -> None:
   key = (device.type, device.index)
   mirror = _status_mirrors.get(key)
   if mirror is None:
-    mirror = (torch.zeros(4, dtype=torch.int32).pin_memory(), torch.cuda.Event())
+    mirror = (torch.zeros(4, dtype=torch.int32).pin_memory(), torch.cuda.Event(), torch.cuda.Stream(device),
+              torch.cuda.Event())
     _status_mirrors[key] = mirror
-  host, event = mirror
-  host.copy_(_status_word(device), non_blocking=True)
-  event.record(torch.cuda.current_stream(device))
+  host, event, side, launched = mirror
+  launched.record(torch.cuda.current_stream(device))
+  side.wait_event(launched)
+  with torch.cuda.stream(side):
+    host.copy_(_status_word(device), non_blocking=True)
+    event.record(side)
 
 
 class _DeviceSchedule(NamedTuple):
