@@ -625,13 +625,17 @@ def run_ours(args):
 
   e2e_ms = float("nan")
   if not args.no_e2e:
-    for i in range(2):
+    # Untimed steps first: they fill the pipeline and let the caching allocator settle on the
+    # result buffers it recycles between the compute and the copy-out stream.
+    e2e_warm = 4
+    for i in range(e2e_warm):
       e2e_step(i)
+    torch.cuda.synchronize(dev)
     barrier()
     e_start, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e_start.record()
     for i in range(args.steps):
-      e2e_step(i + 2)
+      e2e_step(i + e2e_warm)
     compute.wait_event(out_done)  # the last step's results have reached the host
     e_end.record()
     barrier()
